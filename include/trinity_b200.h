@@ -1,0 +1,257 @@
+/*
+ * trinity_b200 — C ABI of the sm_100a kernel backend for Trinity's fused attention-block operators
+ * (Vanilla, PreNorm, QKNorm, KeyFormer, RoCo) and standalone RMSNorm.
+ *
+ * This is the boundary a binding (ctypes, cgo, JNI ...) talks to.  Plain pointers and sizes only; no
+ * torch types.  All pointers are DEVICE pointers unless a name ends in `_host`.  Nothing here
+ * allocates device memory or synchronises the stream unless its comment says so: the caller owns every
+ * buffer, scratch included, exactly as the reference's generated `forward(*tensors)` writes in place
+ * into caller tensors (TritonGen.py:541-714).
+ *
+ * Every entry point returns 0 on success and a negative TRN_E* code when validation fails (nothing is
+ * launched then).  trinity_strerror() turns a code into text.  Kernels record device-side problems
+ * (a bounded wait that ran out) in a status word read with trinity_last_kernel_status().
+ */
+#ifndef TRINITY_B200_H_
+#define TRINITY_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRINITY_ABI_VERSION 1
+
+/* element types of activations / weights / outputs */
+enum { TRN_BF16 = 0, TRN_FP16 = 1 };
+
+/* variants of the attention block (ref_rms.py:29-280) */
+enum {
+  TRN_VANILLA = 0,   /* ref_rms.py:45-83   */
+  TRN_PRENORM = 1,   /* ref_rms.py:101-127 */
+  TRN_QKNORM = 2,    /* ref_rms.py:197-231 */
+  TRN_KEYFORMER = 3, /* ref_rms.py:147-179 */
+  TRN_ROCO = 4       /* ref_rms.py:249-280 */
+};
+
+/* where KeyFormer's additive noise comes from */
+enum {
+  TRN_NOISE_NONE = 0,
+  TRN_NOISE_TENSOR = 1, /* `noise` tensor, the reference's input (convert_eval_rms.py:97,201)      */
+  TRN_NOISE_GUMBEL = 2  /* counter-based Gumbel(0,1) generated in the kernel from `seed`          */
+};
+
+enum {
+  TRN_OK = 0,
+  TRN_E_NULL = -1,      /* a required pointer is NULL                                   */
+  TRN_E_SHAPE = -2,     /* a dimension is zero, negative or not supported by the kernels */
+  TRN_E_ALIGN = -3,     /* a pointer or stride breaks the 16-byte rule of vector / TMA access */
+  TRN_E_DTYPE = -4,     /* unknown element type                                          */
+  TRN_E_VARIANT = -5,   /* unknown variant / flag combination                            */
+  TRN_E_WORKSPACE = -6, /* workspace missing or too small                                */
+  TRN_E_CUDA = -7,      /* a CUDA runtime / driver call failed (see trinity_last_cuda_error) */
+  TRN_E_DEVICE = -8,    /* the current device is not sm_100                               */
+  TRN_E_KERNEL = -9     /* a kernel reported a device-side status (timeout)               */
+};
+
+int trinity_abi_version(void);
+const char* trinity_strerror(int code);
+/* text of the last CUDA error seen by this library on the calling thread ("" if none) */
+const char* trinity_last_cuda_error(void);
+/* Device-side status word of the current device: 0 when every kernel launched so far finished its
+ * waits in time.  SYNCHRONISES the device (it reads device memory); call it outside timed regions. */
+int trinity_last_kernel_status(int* status_out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Standalone RMSNorm:  y[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * gamma[:]
+ * Replaces the reference's X2 / X_norm IR tensors (vanilla_llama_benchmark.py:43-45) and the math of
+ * ref_rms.py:102-103 (eps = 0, gamma = NULL) and ref_attn.py:348-350 (eps, weight).
+ * Reduction in fp32.  `cols` must be a multiple of 8; row strides in elements, multiples of 8.
+ * rstd_out (optional, fp32 [rows]) receives rsqrt(mean + eps).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  void* y;
+  const void* gamma; /* [cols] or NULL */
+  float* rstd_out;   /* [rows] or NULL */
+  int64_t rows, cols;
+  int64_t x_row_stride, y_row_stride;
+  float eps;
+  int dtype;
+} TrnRmsArgs;
+int trinity_rmsnorm(const TrnRmsArgs* a, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Addressing of a head-split activation tensor: element (b, s, h, d) lives at
+ *   base + b*stride_b + s*stride_s + h*stride_h + d        (strides in elements, d contiguous)
+ * which covers the reference's token-major [M, H, D] / [M, N] tensors, its head-major [H, M, D]
+ * tensors and the head-major caches [H, P+M, D] (convert_eval_rms.py:62-108).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  void* ptr;
+  int64_t stride_b, stride_s, stride_h;
+} TrnHeadTensor;
+
+/* ------------------------------------------------------------------------------------------------
+ * QKV projection with fused epilogues (ref_rms.py:47-56, 102-103, 217-220, 72-73):
+ *   q = rowscale * (x @ wq),  k = rowscale * (x @ wk),  v = rowscale * (x @ wv)
+ *   optional per-head RMS norm of q and k over head_dim (QKNorm), then
+ *   q -> q_out, k/v -> rows [P, P+M) of the caches (the reference's cache append).
+ * x: [B*M, N] row-major.  w*: [N, heads*D] row-major, used as x @ w (not transposed, ref_rms.py:47).
+ * row_scale: fp32 [B*M] or NULL (PreNorm's rsqrt(mean x^2 + eps), applied in the epilogue).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  const void* wq;
+  const void* wk;
+  const void* wv;
+  const float* row_scale;
+  int B, M, P, N, Hq, Hkv, D;
+  int dtype;
+  int qk_norm;         /* 1: per-head RMS norm on q and k                 */
+  float qk_eps;
+  const void* gamma_q; /* [D] or NULL */
+  const void* gamma_k; /* [D] or NULL */
+  TrnHeadTensor q;     /* (b, s in [0,M), h in [0,Hq), d)                 */
+  TrnHeadTensor k_cache; /* (b, s in [0,P+M), h in [0,Hkv), d); rows [P,P+M) written */
+  TrnHeadTensor v_cache;
+} TrnProjArgs;
+int trinity_qkv_project(const TrnProjArgs* a, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Attention core (ref_rms.py:72-81): for every (b, query head h) with kv head h / (Hq/Hkv)
+ *   s = scale * q k^T over keys [0, P+M);  causal: query i sees keys j <= P + i
+ *   o = softmax(s) v;  lse (optional) = log-sum-exp of s in base 2:  log2(sum_j 2^(s_ij*log2 e))
+ * When noise_mode != NONE the kernel computes NO output; it writes lse of the perturbed scores
+ *   (s + g) / tau  instead (KeyFormer, ref_rms.py:172-174) — used by trinity_attn_colstats.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  TrnHeadTensor q;       /* s in [0,M)   */
+  TrnHeadTensor k_cache; /* s in [0,P+M) */
+  TrnHeadTensor v_cache;
+  TrnHeadTensor o;       /* s in [0,M); ignored when noise_mode != NONE */
+  float* lse;            /* fp32 [B, Hq, M] or NULL */
+  int B, M, P, Hq, Hkv, D;
+  int dtype;
+  int causal;
+  float scale;
+  int noise_mode;
+  float tau;
+  const void* noise;     /* TRN_NOISE_TENSOR: element (b,h,i,j) at noise + b*nb + h*nh + i*ni + j */
+  int64_t noise_stride_b, noise_stride_h, noise_stride_i;
+  uint64_t seed;
+} TrnAttnArgs;
+int trinity_attention(const TrnAttnArgs* a, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Per-key statistics over queries (RoCo ref_rms.py:274-275, KeyFormer's C_out,
+ * keyformer_llama_benchmark.py:74-79):  with p_ij = 2^(t_ij - lse_i), t = log2(e) * scores
+ * (perturbed scores when noise_mode != NONE), for every (b, h, key j):
+ *   sum_p[b,h,j] = sum_i p_ij        sum_p2[b,h,j] = sum_i p_ij^2   (sum_p2 optional)
+ * Fixed summation order: results are bitwise reproducible run to run.
+ * Outputs are fp32 when stats_fp32 != 0, else `dtype`.  Layout [B, Hq, P+M] contiguous.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  TrnHeadTensor q;
+  TrnHeadTensor k_cache;
+  const float* lse; /* fp32 [B, Hq, M], from trinity_attention */
+  void* sum_p;
+  void* sum_p2;     /* or NULL */
+  int B, M, P, Hq, Hkv, D;
+  int dtype;
+  int stats_fp32;
+  int causal;
+  float scale;
+  int noise_mode;
+  float tau;
+  const void* noise;
+  int64_t noise_stride_b, noise_stride_h, noise_stride_i;
+  uint64_t seed;
+} TrnColStatsArgs;
+int trinity_attn_colstats(const TrnColStatsArgs* a, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Top-k key selection per (b, h) row of an fp32 score matrix [rows, n] (n <= 8192):
+ * indices of the k largest scores, sorted by descending score; equal scores keep the LOWER index
+ * first.  idx_out int32 [rows, k].  No counterpart kernel exists in the reference (its harness only
+ * reports scores); the rule matches torch.sort(descending=True, stable=True)[:k] on the oracle.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const float* scores;
+  int32_t* idx_out;
+  int64_t rows;
+  int n, k;
+  int64_t score_row_stride;
+} TrnTopkArgs;
+int trinity_topk(const TrnTopkArgs* a, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Whole block, the unit the reference's generated forward() computes (TritonGen.py:590-708):
+ *   [PreNorm row statistics] -> QKV projection (+QKNorm, +cache append) -> attention ->
+ *   [KeyFormer / RoCo per-key statistics].
+ * `workspace` holds fp32 row scales [B*M], lse [B,Hq,M] and perturbed lse [B,Hq,M];
+ * trinity_attn_block_workspace() returns the bytes needed (256-byte aligned base required).
+ * skip_projection != 0: q / k_cache / v_cache are taken as given (BASELINE configs 4 and 5).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  int variant;
+  int dtype;
+  int B, M, P, N, Hq, Hkv, D;
+  int skip_projection;
+  const void* x;
+  const void* wq;
+  const void* wk;
+  const void* wv;
+  /* PreNorm */
+  float pre_eps;
+  const void* pre_gamma; /* [N] or NULL; when given, x_norm scratch [B*M, N] must be supplied */
+  void* x_norm;          /* [B*M, N] scratch, required only with pre_gamma */
+  /* QKNorm */
+  float qk_eps;
+  const void* gamma_q;
+  const void* gamma_k;
+  /* tensors */
+  TrnHeadTensor q;
+  TrnHeadTensor k_cache;
+  TrnHeadTensor v_cache;
+  TrnHeadTensor o;
+  int causal;
+  float scale;
+  /* KeyFormer / RoCo */
+  int noise_mode;
+  float tau;
+  const void* noise;
+  int64_t noise_stride_b, noise_stride_h, noise_stride_i;
+  uint64_t seed;
+  void* sum_p;  /* KeyFormer C_out, RoCo C_out1: [B,Hq,P+M] */
+  void* sum_p2; /* RoCo C_out2 or NULL */
+  int stats_fp32;
+  void* workspace;
+  size_t workspace_bytes;
+} TrnBlockArgs;
+size_t trinity_attn_block_workspace(const TrnBlockArgs* a);
+int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Same block with HOST activations: copies x_host -> device staging, runs trinity_attn_block on
+ * `cuda_stream`, copies o back to o_host (and the statistics when the pointers are given) and
+ * synchronises the stream.  x_dev_staging / o (device) are caller buffers as above.  Weights and
+ * caches stay device-resident (they are the model's state, not a per-call input).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  TrnBlockArgs dev;        /* dev.x must point at the device staging buffer for x */
+  const void* x_host;      /* [B*M, N] */
+  void* o_host;            /* same layout and size as dev.o: o_bytes bytes copied */
+  size_t x_bytes, o_bytes;
+  void* sum_p_host;        /* optional */
+  void* sum_p2_host;       /* optional */
+  size_t stats_bytes;
+} TrnBlockHostArgs;
+int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRINITY_B200_H_ */

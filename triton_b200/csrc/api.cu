@@ -1,0 +1,362 @@
+// C ABI of the library (declared in include/trinity_b200.h): argument validation, per-device
+// state, TMA descriptor construction and the composition of the kernels into the whole attention
+// block the reference's generated forward() computes (TritonGen.py:590-708).
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "host.h"
+
+namespace trn {
+
+namespace {
+
+thread_local char g_cuda_err[512] = "";
+
+// Device-side status word: kernels write a non-zero code when a bounded wait ran out.
+// One copy per device that loads this library; addressed through cudaGetSymbolAddress.
+__device__ int g_kernel_status = 0;
+
+constexpr int kMaxDevices = 64;
+DeviceState g_dev[kMaxDevices];
+bool g_dev_ready[kMaxDevices] = {};
+std::mutex g_dev_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int load_encode_fn() {
+  if (g_encode != nullptr) return TRN_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess) return record_cuda_error(e, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+  if (fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled not available from this driver");
+    return TRN_E_CUDA;
+  }
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return TRN_OK;
+}
+
+}  // namespace
+
+int record_cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+  return TRN_E_CUDA;
+}
+
+int record_driver_error(CUresult r, const char* where) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: CUresult %d", where, static_cast<int>(r));
+  return TRN_E_CUDA;
+}
+
+int get_device_state(DeviceState** out) {
+  int dev = -1;
+  TRN_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return TRN_E_DEVICE;
+  std::lock_guard<std::mutex> lock(g_dev_mu);
+  if (!g_dev_ready[dev]) {
+    DeviceState ds;
+    ds.device = dev;
+    TRN_CUDA_TRY(cudaDeviceGetAttribute(&ds.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    TRN_CUDA_TRY(cudaDeviceGetAttribute(&ds.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    if (ds.cc_major != 10) return TRN_E_DEVICE;
+    void* p = nullptr;
+    TRN_CUDA_TRY(cudaGetSymbolAddress(&p, g_kernel_status));
+    ds.status = static_cast<int*>(p);
+    int rc = load_encode_fn();
+    if (rc != TRN_OK) return rc;
+    g_dev[dev] = ds;
+    g_dev_ready[dev] = true;
+  }
+  *out = &g_dev[dev];
+  return TRN_OK;
+}
+
+int make_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                    const uint32_t* box) {
+  if (g_encode == nullptr) {
+    int rc = load_encode_fn();
+    if (rc != TRN_OK) return rc;
+  }
+  if (rank < 2 || rank > 4) return TRN_E_SHAPE;
+  if (!aligned16(base)) return TRN_E_ALIGN;
+  cuuint64_t gdim[4];
+  cuuint64_t gstride[3];
+  cuuint32_t gbox[4];
+  cuuint32_t estride[4];
+  for (int i = 0; i < rank; ++i) {
+    if (dims[i] == 0) return TRN_E_SHAPE;
+    gdim[i] = dims[i];
+    gbox[i] = box[i];
+    estride[i] = 1;
+    if (i >= 1) {
+      const uint64_t bytes = strides[i] * 2ull;
+      if ((bytes & 15ull) != 0) return TRN_E_ALIGN;
+      gstride[i - 1] = bytes;
+    }
+  }
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
+                        gdim, gstride, gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return record_driver_error(r, "cuTensorMapEncodeTiled");
+  return TRN_OK;
+}
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct BlockWorkspace {
+  size_t row_scale_off, lse_off, lse2_off, total;
+};
+
+BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
+  BlockWorkspace w{};
+  size_t off = 0;
+  const size_t rows = static_cast<size_t>(a.B) * a.M;
+  const size_t lse = static_cast<size_t>(a.B) * a.Hq * a.M;
+  w.row_scale_off = off;
+  off += align_up(rows * sizeof(float), 256);
+  w.lse_off = off;
+  off += align_up(lse * sizeof(float), 256);
+  w.lse2_off = off;
+  off += align_up(lse * sizeof(float), 256);
+  w.total = off;
+  return w;
+}
+
+}  // namespace
+}  // namespace trn
+
+using namespace trn;
+
+extern "C" {
+
+int trinity_abi_version(void) { return TRINITY_ABI_VERSION; }
+
+const char* trinity_strerror(int code) {
+  switch (code) {
+    case TRN_OK: return "ok";
+    case TRN_E_NULL: return "a required pointer is NULL";
+    case TRN_E_SHAPE: return "unsupported or inconsistent shape";
+    case TRN_E_ALIGN: return "pointer or stride is not 16-byte aligned";
+    case TRN_E_DTYPE: return "unknown element type";
+    case TRN_E_VARIANT: return "unknown variant or flag combination";
+    case TRN_E_WORKSPACE: return "workspace missing, misaligned or too small";
+    case TRN_E_CUDA: return "a CUDA call failed (see trinity_last_cuda_error)";
+    case TRN_E_DEVICE: return "current device is not an sm_100 GPU";
+    case TRN_E_KERNEL: return "a kernel reported a device-side status (a bounded wait ran out)";
+    default: return "unknown error code";
+  }
+}
+
+const char* trinity_last_cuda_error(void) { return g_cuda_err; }
+
+int trinity_last_kernel_status(int* status_out) {
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  int v = 0;
+  TRN_CUDA_TRY(cudaDeviceSynchronize());
+  TRN_CUDA_TRY(cudaMemcpy(&v, ds->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (status_out != nullptr) *status_out = v;
+  return v == 0 ? TRN_OK : TRN_E_KERNEL;
+}
+
+int trinity_rmsnorm(const TrnRmsArgs* a, void* cuda_stream) {
+  if (a == nullptr) return TRN_E_NULL;
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  return launch_rmsnorm(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
+}
+
+int trinity_qkv_project(const TrnProjArgs* a, void* cuda_stream) {
+  if (a == nullptr) return TRN_E_NULL;
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  return launch_qkv_project(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
+}
+
+int trinity_attention(const TrnAttnArgs* a, void* cuda_stream) {
+  if (a == nullptr) return TRN_E_NULL;
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  return launch_attention(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
+}
+
+int trinity_attn_colstats(const TrnColStatsArgs* a, void* cuda_stream) {
+  if (a == nullptr) return TRN_E_NULL;
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  return launch_colstats(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
+}
+
+int trinity_topk(const TrnTopkArgs* a, void* cuda_stream) {
+  if (a == nullptr) return TRN_E_NULL;
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  return launch_topk(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
+}
+
+size_t trinity_attn_block_workspace(const TrnBlockArgs* a) {
+  if (a == nullptr || a->B <= 0 || a->M <= 0 || a->Hq <= 0) return 0;
+  return block_workspace_layout(*a).total;
+}
+
+int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
+  if (a == nullptr) return TRN_E_NULL;
+  if (a->variant < TRN_VANILLA || a->variant > TRN_ROCO) return TRN_E_VARIANT;
+  if (a->B <= 0 || a->M <= 0 || a->P < 0 || a->Hq <= 0 || a->Hkv <= 0) return TRN_E_SHAPE;
+  if (a->Hq % a->Hkv != 0) return TRN_E_SHAPE;
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+
+  const BlockWorkspace wl = block_workspace_layout(*a);
+  if (a->workspace == nullptr || a->workspace_bytes < wl.total) return TRN_E_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0) return TRN_E_WORKSPACE;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  float* row_scale = reinterpret_cast<float*>(ws + wl.row_scale_off);
+  float* lse = reinterpret_cast<float*>(ws + wl.lse_off);
+  float* lse_pert = reinterpret_cast<float*>(ws + wl.lse2_off);
+
+  const bool stats = (a->variant == TRN_KEYFORMER || a->variant == TRN_ROCO);
+  if (stats && a->sum_p == nullptr) return TRN_E_NULL;
+  if (a->variant == TRN_ROCO && a->sum_p2 == nullptr) return TRN_E_NULL;
+  if (a->variant == TRN_KEYFORMER && a->noise_mode == TRN_NOISE_TENSOR && a->noise == nullptr) return TRN_E_NULL;
+
+  if (!a->skip_projection) {
+    if (a->N <= 0) return TRN_E_SHAPE;
+    const void* x_in = a->x;
+    const float* rs = nullptr;
+    if (a->variant == TRN_PRENORM) {
+      TrnRmsArgs r{};
+      r.x = a->x;
+      r.rows = static_cast<int64_t>(a->B) * a->M;
+      r.cols = a->N;
+      r.x_row_stride = a->N;
+      r.y_row_stride = a->N;
+      r.eps = a->pre_eps;
+      r.dtype = a->dtype;
+      if (a->pre_gamma != nullptr) {
+        // gamma scales the hidden (contraction) axis, so it cannot move to the GEMM epilogue:
+        // materialise x_norm once, then project it.
+        if (a->x_norm == nullptr) return TRN_E_NULL;
+        r.y = a->x_norm;
+        r.gamma = a->pre_gamma;
+        x_in = a->x_norm;
+      } else {
+        // (x * r_i) @ w == r_i * (x @ w): only the row statistics are computed here
+        r.rstd_out = row_scale;
+        rs = row_scale;
+      }
+      rc = launch_rmsnorm(r, st, *ds);
+      if (rc != TRN_OK) return rc;
+    }
+    TrnProjArgs pj{};
+    pj.x = x_in;
+    pj.wq = a->wq;
+    pj.wk = a->wk;
+    pj.wv = a->wv;
+    pj.row_scale = rs;
+    pj.B = a->B; pj.M = a->M; pj.P = a->P; pj.N = a->N;
+    pj.Hq = a->Hq; pj.Hkv = a->Hkv; pj.D = a->D;
+    pj.dtype = a->dtype;
+    pj.qk_norm = (a->variant == TRN_QKNORM) ? 1 : 0;
+    pj.qk_eps = a->qk_eps;
+    pj.gamma_q = a->gamma_q;
+    pj.gamma_k = a->gamma_k;
+    pj.q = a->q;
+    pj.k_cache = a->k_cache;
+    pj.v_cache = a->v_cache;
+    rc = launch_qkv_project(pj, st, *ds);
+    if (rc != TRN_OK) return rc;
+  }
+
+  TrnAttnArgs at{};
+  at.q = a->q;
+  at.k_cache = a->k_cache;
+  at.v_cache = a->v_cache;
+  at.o = a->o;
+  at.lse = stats ? lse : nullptr;
+  at.B = a->B; at.M = a->M; at.P = a->P; at.Hq = a->Hq; at.Hkv = a->Hkv; at.D = a->D;
+  at.dtype = a->dtype;
+  at.causal = a->causal;
+  at.scale = a->scale;
+  at.noise_mode = TRN_NOISE_NONE;
+  at.tau = 1.0f;
+  rc = launch_attention(at, st, *ds);
+  if (rc != TRN_OK) return rc;
+
+  if (stats) {
+    const float* lse_for_stats = lse;
+    int noise_mode = TRN_NOISE_NONE;
+    if (a->variant == TRN_KEYFORMER) {
+      // second row pass: log-sum-exp of the perturbed scores (ref_rms.py:172,174)
+      TrnAttnArgs pt = at;
+      pt.lse = lse_pert;
+      pt.noise_mode = a->noise_mode;
+      pt.tau = a->tau;
+      pt.noise = a->noise;
+      pt.noise_stride_b = a->noise_stride_b;
+      pt.noise_stride_h = a->noise_stride_h;
+      pt.noise_stride_i = a->noise_stride_i;
+      pt.seed = a->seed;
+      if (pt.noise_mode == TRN_NOISE_NONE) return TRN_E_VARIANT;
+      rc = launch_attention(pt, st, *ds);
+      if (rc != TRN_OK) return rc;
+      lse_for_stats = lse_pert;
+      noise_mode = a->noise_mode;
+    }
+    TrnColStatsArgs cs{};
+    cs.q = a->q;
+    cs.k_cache = a->k_cache;
+    cs.lse = lse_for_stats;
+    cs.sum_p = a->sum_p;
+    cs.sum_p2 = (a->variant == TRN_ROCO) ? a->sum_p2 : nullptr;
+    cs.B = a->B; cs.M = a->M; cs.P = a->P; cs.Hq = a->Hq; cs.Hkv = a->Hkv; cs.D = a->D;
+    cs.dtype = a->dtype;
+    cs.stats_fp32 = a->stats_fp32;
+    cs.causal = a->causal;
+    cs.scale = a->scale;
+    cs.noise_mode = noise_mode;
+    cs.tau = (a->variant == TRN_KEYFORMER) ? a->tau : 1.0f;
+    cs.noise = a->noise;
+    cs.noise_stride_b = a->noise_stride_b;
+    cs.noise_stride_h = a->noise_stride_h;
+    cs.noise_stride_i = a->noise_stride_i;
+    cs.seed = a->seed;
+    rc = launch_colstats(cs, st, *ds);
+    if (rc != TRN_OK) return rc;
+  }
+  return TRN_OK;
+}
+
+int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream) {
+  if (a == nullptr || a->x_host == nullptr || a->o_host == nullptr) return TRN_E_NULL;
+  if (a->dev.x == nullptr || a->dev.o.ptr == nullptr) return TRN_E_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  TRN_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(a->dev.x), a->x_host, a->x_bytes, cudaMemcpyHostToDevice, st));
+  int rc = trinity_attn_block(&a->dev, cuda_stream);
+  if (rc != TRN_OK) return rc;
+  TRN_CUDA_TRY(cudaMemcpyAsync(a->o_host, a->dev.o.ptr, a->o_bytes, cudaMemcpyDeviceToHost, st));
+  if (a->sum_p_host != nullptr && a->dev.sum_p != nullptr)
+    TRN_CUDA_TRY(cudaMemcpyAsync(a->sum_p_host, a->dev.sum_p, a->stats_bytes, cudaMemcpyDeviceToHost, st));
+  if (a->sum_p2_host != nullptr && a->dev.sum_p2 != nullptr)
+    TRN_CUDA_TRY(cudaMemcpyAsync(a->sum_p2_host, a->dev.sum_p2, a->stats_bytes, cudaMemcpyDeviceToHost, st));
+  TRN_CUDA_TRY(cudaStreamSynchronize(st));
+  return TRN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,51 @@
+// Host-side plumbing shared by the .cu files: error recording, the per-device status word,
+// device checks and TMA descriptor (CUtensorMap) construction through the driver entry point.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/trinity_b200.h"
+
+namespace trn {
+
+// records the CUDA error text for trinity_last_cuda_error(); returns TRN_E_CUDA
+int record_cuda_error(cudaError_t e, const char* where);
+int record_driver_error(CUresult r, const char* where);
+
+#define TRN_CUDA_TRY(expr)                                          \
+  do {                                                              \
+    cudaError_t _e = (expr);                                        \
+    if (_e != cudaSuccess) return ::trn::record_cuda_error(_e, #expr); \
+  } while (0)
+
+// Per-device state created on first use (outside stream capture: the first call on a device
+// allocates one int of device memory for the status word).
+struct DeviceState {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0;
+  int* status = nullptr;   // device int, zero-initialised
+};
+// returns TRN_OK and fills *out, or an error code (TRN_E_DEVICE when not sm_100)
+int get_device_state(DeviceState** out);
+
+// Tiled tensor map over a tensor of 16-bit elements with up to 4 dims (dim 0 contiguous),
+// 128-byte swizzle, zero fill outside the tensor.
+//   dims[i]    extent of dim i (elements)
+//   strides[i] stride of dim i in ELEMENTS for i >= 1 (dim 0 has stride 1)
+//   box[i]     tile extent of dim i
+int make_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                    const uint32_t* box);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// launchers implemented per kernel family
+int launch_rmsnorm(const TrnRmsArgs& a, cudaStream_t st, const DeviceState& ds);
+int launch_qkv_project(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds);
+int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
+int launch_colstats(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds);
+int launch_topk(const TrnTopkArgs& a, cudaStream_t st, const DeviceState& ds);
+
+}  // namespace trn

@@ -1,0 +1,377 @@
+// QKV projection on the 5th-gen tensor cores:  [q | k | v] = rowscale * (x @ [wq | wk | wv])
+// with the epilogues the attention block needs fused in (ref_rms.py:47-56, 102-103, 217-220, 72-73):
+//   * PreNorm's per-row rsqrt(mean x^2 + eps) applied to the accumulator row,
+//   * QKNorm's per-(token, head) RMS norm over head_dim (+ gamma) on q and k,
+//   * head-split scatter: q to the caller's q tensor, k / v appended at rows [P, P+M) of the caches.
+//
+// Shape of the kernel: persistent, one CTA per SM, 128 x 256 output tile, K step 64.
+//   warp 0     TMA producer: x tile [128 x 64] (K-major) and w tile [64 x 256] (four 64-column
+//              blocks, MN-major: w is used as x @ w so N is its contiguous dim) into a 4-stage ring
+//   warp 1     allocates TMEM, one lane issues tcgen05.mma 128x256x16 (fp32 accumulators in TMEM,
+//              two accumulator buffers of 256 columns so the epilogue overlaps the next tile)
+//   warps 2-5  epilogue: tcgen05.ld the accumulator rows, scale / normalise, pack to 16-bit and
+//              store 64-byte runs per thread
+// The three weight matrices are separate tensors, so the tile space is three "segments", each with
+// its own TMA descriptor and output addressing.
+//
+// Algorithmic work per launch: 2 * rows * N * (Hq + 2 Hkv) * D flops;
+// compulsory bytes: x + wq + wk + wv + q + k + v once each.
+#include "common.cuh"
+#include "host.h"
+
+namespace trn {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;          // 16 KiB
+constexpr int kBBlockBytes = BK * 64 * 2;     // one 64-column block of w: 64 rows x 128 B = 8 KiB
+constexpr int kBBytes = kBBlockBytes * (BN / 64);
+constexpr int kStageBytes = kABytes + kBBytes;   // 48 KiB
+constexpr int kTmemCols = 512;                // 2 accumulators x 256 fp32 columns
+constexpr int kThreads = 192;
+constexpr int kBarBytes = 256;
+constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;   // +1024: manual 1 KiB alignment
+constexpr int kGroupM = 8;                    // m-tiles per raster group (L2 reuse of the w columns)
+
+struct Seg {
+  void* out;
+  const void* gamma;
+  long long stride_b, stride_s, stride_h;
+  int n;         // columns of this weight matrix (heads * D)
+  int n_tiles;   // ceil(n / BN)
+  int tile0;     // first n-tile index of this segment in the concatenated tile space
+  int row_off;   // position offset of row 0 inside the output (P for the caches, 0 for q)
+  int norm;      // per-head RMS norm in the epilogue
+};
+
+struct GemmParams {
+  Seg seg[3];
+  const float* row_scale;
+  int rows;            // B * M
+  int rows_per_batch;  // M
+  int K;               // hidden size N of the block
+  int D;               // head_dim
+  int m_tiles, n_tiles_total, total_tiles;
+  float qk_eps;
+  int* status;
+};
+
+struct TileCoord {
+  int m_tile, seg, n_tile;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
+  const int per_group = kGroupM * p.n_tiles_total;
+  const int grp = t / per_group;
+  const int r = t - grp * per_group;
+  const int m0 = grp * kGroupM;
+  const int gsz = min(kGroupM, p.m_tiles - m0);
+  const int nt = r / gsz;
+  TileCoord c;
+  c.m_tile = m0 + (r - nt * gsz);
+  c.seg = (nt >= p.seg[2].tile0) ? 2 : (nt >= p.seg[1].tile0 ? 1 : 0);
+  c.n_tile = nt - p.seg[c.seg].tile0;
+  return c;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w0,
+                const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2,
+                const __grid_constant__ GemmParams p) {
+  // an earlier CTA / kernel gave up: leave before touching barriers or TMEM (decision is CTA-uniform)
+  __shared__ int s_skip;
+  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (s_skip != 0) return;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages * kStageBytes;
+  // barrier layout (8 bytes each): full[4], empty[4], tmem_full[2], tmem_empty[2], then tmem ptr, abort
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  volatile uint32_t* tmem_ptr_smem =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * kStageBytes + 8 * (2 * kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  Ctl ctl{p.status, abort_flag};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int k_steps = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_x);
+      tma_prefetch_desc(&tm_w0);
+      tma_prefetch_desc(&tm_w1);
+      tma_prefetch_desc(&tm_w2);
+    }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      const TileCoord tc = decode_tile(p, t);
+      const CUtensorMap* tm_w = tc.seg == 0 ? &tm_w0 : (tc.seg == 1 ? &tm_w1 : &tm_w2);
+      for (int ks = 0; ks < k_steps; ++ks) {
+        ok = mbar_wait(empty_bar(stage), phase ^ 1u, ctl, KST_TIMEOUT_PRODUCER);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+          mbar_expect_tx(full_bar(stage), kStageBytes);
+          tma_load_2d(sa, &tm_x, full_bar(stage), ks * BK, tc.m_tile * BM);
+#pragma unroll
+          for (int c = 0; c < BN / 64; ++c)
+            tma_load_2d(sb + c * kBBlockBytes, tm_w, full_bar(stage), tc.n_tile * BN + c * 64, ks * BK);
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    constexpr uint32_t idesc = make_idesc_f16(Io<T>::kFmt, /*a_mn=*/0, /*b_mn=*/1, BM, BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int it = 0;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, KST_TIMEOUT_MMA);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int ks = 0; ks < k_steps; ++ks) {
+        ok = mbar_wait(full_bar(stage), phase, ctl, KST_TIMEOUT_MMA);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // x tile: K-major, 16 K-elements = 32 bytes inside the 128-byte swizzled row
+            const uint64_t adesc = make_smem_desc(sa + kk * 32, 0, 1024);
+            // w tile: MN-major, 16 K-rows = 2 KiB; 64-column blocks 8 KiB apart
+            const uint64_t bdesc = make_smem_desc(sb + kk * 2048, kBBlockBytes, 1024);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (ks | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));   // frees the stage when these MMAs have read it
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit(tfull_bar(acc));
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------- epilogue (warps 2..5) -------------------------------
+    const int quad = warp & 3;                   // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    const int r_in_tile = quad * 32 + lane;
+    const int heads_per_tile = BN / p.D;
+    const int chunks_per_head = p.D / 32;
+    const float inv_d = 1.0f / static_cast<float>(p.D);
+    bool ok = true;
+    int it = 0;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+      const TileCoord tc = decode_tile(p, t);
+      const Seg& sg = p.seg[tc.seg];
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(tfull_bar(acc), acc_phase, ctl, KST_TIMEOUT_CONSUMER);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+
+      const int row = tc.m_tile * BM + r_in_tile;
+      const bool valid_row = row < p.rows;
+      const int b = valid_row ? row / p.rows_per_batch : 0;
+      const int s = valid_row ? row - b * p.rows_per_batch : 0;
+      const float rscale = (valid_row && p.row_scale != nullptr) ? __ldg(p.row_scale + row) : 1.0f;
+      T* out_row = static_cast<T*>(sg.out) + static_cast<long long>(b) * sg.stride_b +
+                   static_cast<long long>(sg.row_off + s) * sg.stride_s;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+
+      for (int hh = 0; hh < heads_per_tile; ++hh) {
+        const int col0 = tc.n_tile * BN + hh * p.D;
+        if (col0 >= sg.n) break;
+        const int h = col0 / p.D;
+        float rs = rscale;
+        uint32_t r[32];
+        if (sg.norm) {
+          float ss = 0.f;
+          for (int c = 0; c < chunks_per_head; ++c) {
+            tmem_ld32(t_row + hh * p.D + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = __uint_as_float(r[i]) * rscale;
+              ss = fmaf(v, v, ss);
+            }
+          }
+          rs = rscale * rsqrtf(ss * inv_d + p.qk_eps);
+        }
+        T* out_head = out_row + static_cast<long long>(h) * sg.stride_h;
+        for (int c = 0; c < chunks_per_head; ++c) {
+          tmem_ld32(t_row + hh * p.D + c * 32, r);
+          tmem_wait_ld();
+          if (valid_row) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[i + j]) * rs;
+              if (sg.gamma != nullptr) {
+                const uint4 g = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(sg.gamma) + c * 32 + i));
+                const float2 g0 = Io<T>::unpack2(g.x), g1 = Io<T>::unpack2(g.y);
+                const float2 g2 = Io<T>::unpack2(g.z), g3 = Io<T>::unpack2(g.w);
+                f[0] *= g0.x; f[1] *= g0.y; f[2] *= g1.x; f[3] *= g1.y;
+                f[4] *= g2.x; f[5] *= g2.y; f[6] *= g3.x; f[7] *= g3.y;
+              }
+              uint4 o;
+              o.x = Io<T>::pack2(f[0], f[1]); o.y = Io<T>::pack2(f[2], f[3]);
+              o.z = Io<T>::pack2(f[4], f[5]); o.w = Io<T>::pack2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(out_head + c * 32 + i) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait ran out: give copies / MMAs in flight time to land before the CTA's memory is reused
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <typename T>
+int launch_typed(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
+  GemmParams p{};
+  const int rows = a.B * a.M;
+  p.rows = rows;
+  p.rows_per_batch = a.M;
+  p.K = a.N;
+  p.D = a.D;
+  p.row_scale = a.row_scale;
+  p.qk_eps = a.qk_eps;
+  p.status = ds.status;
+  p.m_tiles = (rows + BM - 1) / BM;
+
+  const void* w[3] = {a.wq, a.wk, a.wv};
+  const TrnHeadTensor* outs[3] = {&a.q, &a.k_cache, &a.v_cache};
+  const int heads[3] = {a.Hq, a.Hkv, a.Hkv};
+  const void* gam[3] = {a.gamma_q, a.gamma_k, nullptr};
+  CUtensorMap tm_w[3];
+  int tile0 = 0;
+  for (int i = 0; i < 3; ++i) {
+    Seg& s = p.seg[i];
+    s.out = outs[i]->ptr;
+    s.stride_b = outs[i]->stride_b;
+    s.stride_s = outs[i]->stride_s;
+    s.stride_h = outs[i]->stride_h;
+    s.n = heads[i] * a.D;
+    s.n_tiles = (s.n + BN - 1) / BN;
+    s.tile0 = tile0;
+    tile0 += s.n_tiles;
+    s.row_off = (i == 0) ? 0 : a.P;
+    s.norm = (a.qk_norm && i < 2) ? 1 : 0;
+    s.gamma = s.norm ? gam[i] : nullptr;
+    const uint64_t dims[2] = {static_cast<uint64_t>(s.n), static_cast<uint64_t>(a.N)};
+    const uint64_t strides[2] = {1, static_cast<uint64_t>(s.n)};
+    const uint32_t box[2] = {64, BK};
+    int rc = make_tmap_16bit(&tm_w[i], w[i], 2, dims, strides, box);
+    if (rc != TRN_OK) return rc;
+  }
+  p.n_tiles_total = tile0;
+  p.total_tiles = p.m_tiles * p.n_tiles_total;
+
+  CUtensorMap tm_x;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(rows)};
+    const uint64_t strides[2] = {1, static_cast<uint64_t>(a.N)};
+    const uint32_t box[2] = {BK, BM};
+    int rc = make_tmap_16bit(&tm_x, a.x, 2, dims, strides, box);
+    if (rc != TRN_OK) return rc;
+  }
+
+  static bool attr_set[2] = {false, false};
+  auto kern = qkv_gemm_kernel<T>;
+  if (!attr_set[Io<T>::kFmt]) {
+    TRN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    attr_set[Io<T>::kFmt] = true;
+  }
+  const int grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
+  kern<<<grid, kThreads, kSmemBytes, st>>>(tm_x, tm_w[0], tm_w[1], tm_w[2], p);
+  TRN_CUDA_TRY(cudaGetLastError());
+  return TRN_OK;
+}
+
+bool head_tensor_ok(const TrnHeadTensor& t) {
+  return t.ptr != nullptr && aligned16(t.ptr) && (t.stride_b & 7) == 0 && (t.stride_s & 7) == 0 &&
+         (t.stride_h & 7) == 0;
+}
+
+}  // namespace
+
+int launch_qkv_project(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
+  if (a.x == nullptr || a.wq == nullptr || a.wk == nullptr || a.wv == nullptr) return TRN_E_NULL;
+  if (a.q.ptr == nullptr || a.k_cache.ptr == nullptr || a.v_cache.ptr == nullptr) return TRN_E_NULL;
+  if (a.B <= 0 || a.M <= 0 || a.P < 0 || a.N <= 0 || a.Hq <= 0 || a.Hkv <= 0) return TRN_E_SHAPE;
+  if (a.D != 64 && a.D != 128) return TRN_E_SHAPE;
+  if ((a.N & 7) != 0) return TRN_E_SHAPE;
+  if (static_cast<long long>(a.B) * a.M > 0x7fffffffLL) return TRN_E_SHAPE;
+  if (!aligned16(a.x) || !aligned16(a.wq) || !aligned16(a.wk) || !aligned16(a.wv)) return TRN_E_ALIGN;
+  if (!aligned16(a.gamma_q) || !aligned16(a.gamma_k)) return TRN_E_ALIGN;
+  if (!head_tensor_ok(a.q) || !head_tensor_ok(a.k_cache) || !head_tensor_ok(a.v_cache)) return TRN_E_ALIGN;
+  if (a.dtype == TRN_BF16) return launch_typed<__nv_bfloat16>(a, st, ds);
+  if (a.dtype == TRN_FP16) return launch_typed<__half>(a, st, ds);
+  return TRN_E_DTYPE;
+}
+
+}  // namespace trn

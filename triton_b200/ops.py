@@ -1,0 +1,233 @@
+"""Operators of the attention block on torch CUDA tensors, each a thin call into the C-ABI library.
+
+torch is used for device memory and the current stream only; every computation is done by the
+sm_100a kernels behind include/trinity_b200.h.  All operators write into caller-provided tensors
+and launch on ``torch.cuda.current_stream()`` without synchronising, so a sequence of them can be
+captured in a CUDA graph exactly like the reference's generated ``forward``
+(vanilla_llama_benchmark.py:263-285).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+
+_DTYPES = {torch.bfloat16: L.TRN_BF16, torch.float16: L.TRN_FP16}
+
+# layout strings name the dims of a tensor in memory order; the kernels see (b, s, h, d) strides
+_LAYOUT_PERM = {
+    "bshd": (0, 1, 2, 3),
+    "bhsd": (0, 2, 1, 3),
+    "shd": None,   # handled by unsqueeze
+    "hsd": None,
+}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"triton_b200 kernels take bfloat16 or float16 tensors, got {t.dtype}") from None
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("triton_b200 operators need CUDA tensors (there is no CPU path)")
+
+
+def as_bshd(t: torch.Tensor, layout: str) -> torch.Tensor:
+    """View of ``t`` with dims (batch, position, head, head_dim), whatever its memory layout."""
+    if layout == "bshd":
+        v = t
+    elif layout == "bhsd":
+        v = t.permute(0, 2, 1, 3)
+    elif layout == "shd":
+        v = t.unsqueeze(0)
+    elif layout == "hsd":
+        v = t.unsqueeze(0).permute(0, 2, 1, 3)
+    else:
+        raise ValueError(f"unknown layout {layout!r}")
+    if v.dim() != 4 or v.stride(3) != 1:
+        raise ValueError(f"tensor of shape {tuple(t.shape)} does not fit layout {layout!r} with contiguous head_dim")
+    return v
+
+
+def _head_tensor(v: Optional[torch.Tensor]) -> L.TrnHeadTensor:
+    if v is None:
+        return L.TrnHeadTensor(None, 0, 0, 0)
+    return L.TrnHeadTensor(v.data_ptr(), v.stride(0), v.stride(1), v.stride(2))
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def rmsnorm(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, eps: float = 0.0,
+            out: Optional[torch.Tensor] = None, rstd_out: Optional[torch.Tensor] = None,
+            stats_only: bool = False) -> Optional[torch.Tensor]:
+    """y = x * rsqrt(mean(x^2, -1) + eps) * gamma over the last dim of a 2-D (or flattenable) tensor."""
+    _need_cuda(x, gamma, out, rstd_out)
+    x2 = x.reshape(-1, x.shape[-1]) if x.dim() != 2 else x
+    if x2.stride(1) != 1:
+        raise ValueError("rmsnorm needs a contiguous last dim")
+    if out is None and not stats_only:
+        out = torch.empty_like(x)
+    y2 = None
+    if out is not None:
+        y2 = out.reshape(-1, out.shape[-1]) if out.dim() != 2 else out
+        if y2.shape != x2.shape or y2.dtype != x2.dtype or y2.stride(1) != 1:
+            raise ValueError("rmsnorm output must match the input's shape and dtype")
+    if rstd_out is not None and (rstd_out.dtype != torch.float32 or rstd_out.numel() < x2.shape[0]):
+        raise ValueError("rstd_out must be float32 with one entry per row")
+    a = L.TrnRmsArgs(x2.data_ptr(), _ptr(y2), _ptr(gamma), _ptr(rstd_out), x2.shape[0], x2.shape[1],
+                     x2.stride(0), y2.stride(0) if y2 is not None else x2.shape[1], float(eps), _dtype_code(x2))
+    L.check(L.load().trinity_rmsnorm(C.byref(a), _stream()))
+    return out
+
+
+def qkv_project(x: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, *,
+                q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                B: int, M: int, P: int, Hq: int, Hkv: int, D: int,
+                row_scale: Optional[torch.Tensor] = None, qk_norm: bool = False, qk_eps: float = 0.0,
+                gamma_q: Optional[torch.Tensor] = None, gamma_k: Optional[torch.Tensor] = None) -> None:
+    """q, k, v = x @ wq, x @ wk, x @ wv with fused row scale / per-head norm; k, v land at rows
+    [P, P+M) of the caches.  ``q``, ``k_cache``, ``v_cache`` are (b, s, h, d) views (see as_bshd)."""
+    _need_cuda(x, wq, wk, wv, q, k_cache, v_cache, row_scale, gamma_q, gamma_k)
+    N = x.shape[-1]
+    if not (x.is_contiguous() and wq.is_contiguous() and wk.is_contiguous() and wv.is_contiguous()):
+        raise ValueError("x and the weights must be contiguous")
+    if wq.shape != (N, Hq * D) or wk.shape != (N, Hkv * D) or wv.shape != (N, Hkv * D):
+        raise ValueError("weight shapes must be [N, heads*D] (used as x @ w)")
+    if x.numel() != B * M * N:
+        raise ValueError("x must hold B*M rows of N")
+    a = L.TrnProjArgs(x.data_ptr(), wq.data_ptr(), wk.data_ptr(), wv.data_ptr(), _ptr(row_scale),
+                      B, M, P, N, Hq, Hkv, D, _dtype_code(x), int(qk_norm), float(qk_eps),
+                      _ptr(gamma_q), _ptr(gamma_k), _head_tensor(q), _head_tensor(k_cache), _head_tensor(v_cache))
+    L.check(L.load().trinity_qkv_project(C.byref(a), _stream()))
+
+
+def _noise_fields(noise: Optional[torch.Tensor]):
+    """noise is a (b, h, i, j) view with contiguous j."""
+    if noise is None:
+        return None, 0, 0, 0
+    if noise.dim() != 4 or noise.stride(3) != 1:
+        raise ValueError("noise must be a 4-D (b, h, query, key) view with contiguous keys")
+    return noise.data_ptr(), noise.stride(0), noise.stride(1), noise.stride(2)
+
+
+def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o: Optional[torch.Tensor], *,
+              P: int, causal: bool, scale: float, lse: Optional[torch.Tensor] = None,
+              noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
+              seed: int = 0) -> None:
+    """o = softmax(scale * q k^T [causal]) v over keys [0, P+M).  All tensors are (b, s, h, d) views."""
+    _need_cuda(q, k_cache, v_cache, o, lse, noise)
+    B, M, Hq, D = q.shape
+    Hkv = k_cache.shape[2]
+    if k_cache.shape[1] < P + M or v_cache.shape[1] < P + M:
+        raise ValueError("caches must hold P+M positions")
+    nptr, nb, nh, ni = _noise_fields(noise)
+    a = L.TrnAttnArgs(_head_tensor(q), _head_tensor(k_cache), _head_tensor(v_cache), _head_tensor(o), _ptr(lse),
+                      B, M, P, Hq, Hkv, D, _dtype_code(q), int(causal), float(scale), noise_mode, float(tau),
+                      nptr, nb, nh, ni, seed)
+    L.check(L.load().trinity_attention(C.byref(a), _stream()))
+
+
+def attn_colstats(q: torch.Tensor, k_cache: torch.Tensor, lse: torch.Tensor, sum_p: torch.Tensor,
+                  sum_p2: Optional[torch.Tensor] = None, *, P: int, causal: bool, scale: float,
+                  noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
+                  seed: int = 0) -> None:
+    """Per-key sums over queries of the attention probabilities (and of their squares)."""
+    _need_cuda(q, k_cache, lse, sum_p, sum_p2, noise)
+    B, M, Hq, D = q.shape
+    Hkv = k_cache.shape[2]
+    nptr, nb, nh, ni = _noise_fields(noise)
+    a = L.TrnColStatsArgs(_head_tensor(q), _head_tensor(k_cache), lse.data_ptr(), sum_p.data_ptr(), _ptr(sum_p2),
+                          B, M, P, Hq, Hkv, D, _dtype_code(q), int(sum_p.dtype == torch.float32), int(causal),
+                          float(scale), noise_mode, float(tau), nptr, nb, nh, ni, seed)
+    L.check(L.load().trinity_attn_colstats(C.byref(a), _stream()))
+
+
+def topk_keys(scores: torch.Tensor, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Indices of the k largest entries of each row of ``scores`` ([..., n] fp32), descending, ties
+    to the lower index."""
+    _need_cuda(scores, out)
+    if scores.dtype != torch.float32 or scores.stride(-1) != 1:
+        raise ValueError("scores must be float32 with a contiguous last dim")
+    s2 = scores.reshape(-1, scores.shape[-1])
+    if out is None:
+        out = torch.empty(*scores.shape[:-1], k, dtype=torch.int32, device=scores.device)
+    a = L.TrnTopkArgs(s2.data_ptr(), out.data_ptr(), s2.shape[0], s2.shape[1], k, s2.stride(0))
+    L.check(L.load().trinity_topk(C.byref(a), _stream()))
+    return out
+
+
+class BlockPlan:
+    """Arguments of one attention block bound once (pointers, strides, workspace), launched many times.
+
+    Construction validates shapes and allocates the workspace through torch — do it before CUDA-graph
+    capture.  ``run()`` only fills nothing and launches: it is what gets captured / replayed.
+    """
+
+    def __init__(self, variant: str, *, B: int, M: int, P: int, Hq: int, Hkv: int, D: int,
+                 q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o: torch.Tensor,
+                 x: Optional[torch.Tensor] = None, wq: Optional[torch.Tensor] = None,
+                 wk: Optional[torch.Tensor] = None, wv: Optional[torch.Tensor] = None,
+                 causal: bool = False, scale: float = 1.0,
+                 pre_eps: float = 0.0, pre_gamma: Optional[torch.Tensor] = None,
+                 qk_eps: float = 0.0, gamma_q: Optional[torch.Tensor] = None,
+                 gamma_k: Optional[torch.Tensor] = None,
+                 noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
+                 seed: int = 0, sum_p: Optional[torch.Tensor] = None, sum_p2: Optional[torch.Tensor] = None):
+        _need_cuda(q, k_cache, v_cache, o, x, wq, wk, wv, pre_gamma, gamma_q, gamma_k, noise, sum_p, sum_p2)
+        self.variant = variant
+        skip = x is None
+        N = 0 if skip else x.shape[-1]
+        a = L.TrnBlockArgs()
+        a.variant = L.VARIANTS[variant]
+        a.dtype = _dtype_code(q)
+        a.B, a.M, a.P, a.N, a.Hq, a.Hkv, a.D = B, M, P, N, Hq, Hkv, D
+        a.skip_projection = int(skip)
+        self._keep = [q, k_cache, v_cache, o, x, wq, wk, wv, pre_gamma, gamma_q, gamma_k, noise, sum_p, sum_p2]
+        if not skip:
+            if not (x.is_contiguous() and wq.is_contiguous() and wk.is_contiguous() and wv.is_contiguous()):
+                raise ValueError("x and the weights must be contiguous")
+            if wq.shape != (N, Hq * D) or wk.shape != (N, Hkv * D) or wv.shape != (N, Hkv * D):
+                raise ValueError("weight shapes must be [N, heads*D] (used as x @ w)")
+            a.x, a.wq, a.wk, a.wv = x.data_ptr(), wq.data_ptr(), wk.data_ptr(), wv.data_ptr()
+        a.pre_eps = float(pre_eps)
+        a.pre_gamma = _ptr(pre_gamma)
+        if pre_gamma is not None and not skip:
+            self._x_norm = torch.empty_like(x)
+            a.x_norm = self._x_norm.data_ptr()
+        a.qk_eps = float(qk_eps)
+        a.gamma_q, a.gamma_k = _ptr(gamma_q), _ptr(gamma_k)
+        a.q, a.k_cache, a.v_cache, a.o = (_head_tensor(q), _head_tensor(k_cache), _head_tensor(v_cache),
+                                          _head_tensor(o))
+        a.causal, a.scale = int(causal), float(scale)
+        a.noise_mode, a.tau = int(noise_mode), float(tau)
+        a.noise, a.noise_stride_b, a.noise_stride_h, a.noise_stride_i = _noise_fields(noise)
+        a.seed = seed
+        a.sum_p, a.sum_p2 = _ptr(sum_p), _ptr(sum_p2)
+        a.stats_fp32 = int(sum_p is not None and sum_p.dtype == torch.float32)
+        lib = L.load()
+        nbytes = lib.trinity_attn_block_workspace(C.byref(a))
+        self._ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
+        a.workspace, a.workspace_bytes = self._ws.data_ptr(), self._ws.numel()
+        self.args = a
+        self._lib = lib
+
+    def run(self) -> None:
+        L.check(self._lib.trinity_attn_block(C.byref(self.args), _stream()))
+
+
+def default_scale(D: int) -> float:
+    return 1.0 / math.sqrt(D)
