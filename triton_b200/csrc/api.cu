@@ -107,6 +107,19 @@ int make_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t
   return TRN_OK;
 }
 
+int ensure_dyn_smem(const void* kernel, int bytes, int device) {
+  struct Entry { const void* k; int dev; };
+  static Entry done[256];
+  static int n_done = 0;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_done; ++i)
+    if (done[i].k == kernel && done[i].dev == device) return TRN_OK;
+  TRN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (n_done < 256) done[n_done++] = Entry{kernel, device};
+  return TRN_OK;
+}
+
 namespace {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }

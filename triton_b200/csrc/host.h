@@ -39,6 +39,9 @@ int get_device_state(DeviceState** out);
 int make_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
                     const uint32_t* box);
 
+// opts a kernel in to `bytes` of dynamic shared memory, once per (kernel, device)
+int ensure_dyn_smem(const void* kernel, int bytes, int device);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // launchers implemented per kernel family

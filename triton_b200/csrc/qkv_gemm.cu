@@ -340,11 +340,10 @@ int launch_typed(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
     if (rc != TRN_OK) return rc;
   }
 
-  static bool attr_set[2] = {false, false};
   auto kern = qkv_gemm_kernel<T>;
-  if (!attr_set[Io<T>::kFmt]) {
-    TRN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    attr_set[Io<T>::kFmt] = true;
+  {
+    int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), kSmemBytes, ds.device);
+    if (rc != TRN_OK) return rc;
   }
   const int grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
   kern<<<grid, kThreads, kSmemBytes, st>>>(tm_x, tm_w[0], tm_w[1], tm_w[2], p);

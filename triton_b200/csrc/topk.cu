@@ -52,7 +52,7 @@ topk_rows_kernel(const float* __restrict__ scores, int32_t* __restrict__ idx_out
 
 }  // namespace
 
-int launch_topk(const TrnTopkArgs& a, cudaStream_t st, const DeviceState&) {
+int launch_topk(const TrnTopkArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (a.scores == nullptr || a.idx_out == nullptr) return TRN_E_NULL;
   if (a.rows < 0 || a.n <= 0 || a.n > kTopkMaxN || a.k <= 0 || a.k > a.n) return TRN_E_SHAPE;
   if (a.score_row_stride < a.n || a.rows > 0x7fffffffLL) return TRN_E_SHAPE;
@@ -60,11 +60,10 @@ int launch_topk(const TrnTopkArgs& a, cudaStream_t st, const DeviceState&) {
   int np2 = 2;
   while (np2 < a.n) np2 <<= 1;
   const size_t smem = static_cast<size_t>(np2) * sizeof(unsigned long long);
-  static bool attr_set = false;
-  if (!attr_set) {
-    TRN_CUDA_TRY(cudaFuncSetAttribute(topk_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kTopkMaxN * static_cast<int>(sizeof(unsigned long long))));
-    attr_set = true;
+  {
+    int rc = ensure_dyn_smem(reinterpret_cast<const void*>(topk_rows_kernel),
+                             kTopkMaxN * static_cast<int>(sizeof(unsigned long long)), ds.device);
+    if (rc != TRN_OK) return rc;
   }
   topk_rows_kernel<<<static_cast<int>(a.rows), kTopkThreads, smem, st>>>(a.scores, a.idx_out, a.n, np2, a.k,
                                                                          a.score_row_stride);
