@@ -142,6 +142,8 @@ typedef struct {
   const void* noise;     /* TRN_NOISE_TENSOR: element (b,h,i,j) at noise + b*nb + h*nh + i*ni + j */
   int64_t noise_stride_b, noise_stride_h, noise_stride_i;
   uint64_t seed;
+  int single_p;          /* 0 (default): p is carried as hi + lo 16-bit parts into the P v product;
+                            1: one 16-bit part only (faster, ~8 / 11 mantissa bits of p)            */
 } TrnAttnArgs;
 int trinity_attention(const TrnAttnArgs* a, void* cuda_stream);
 
@@ -228,6 +230,7 @@ typedef struct {
   void* sum_p;  /* KeyFormer C_out, RoCo C_out1: [B,Hq,P+M] */
   void* sum_p2; /* RoCo C_out2 or NULL */
   int stats_fp32;
+  int single_p; /* see TrnAttnArgs */
   void* workspace;
   size_t workspace_bytes;
 } TrnBlockArgs;

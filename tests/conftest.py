@@ -1,0 +1,53 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (sm_100a) GPU; run with `-m gpu`")
+
+
+def pytest_collection_modifyitems(config, items):
+    # GPU tests are skipped (not failed) where no GPU is visible and the run did not ask for them
+    try:
+        import torch
+        has_gpu = torch.cuda.is_available()
+    except Exception:
+        has_gpu = False
+    if has_gpu:
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+# ---- tolerance of the floating-point parity tests -------------------------------------------------
+# 16-bit kernels against the fp32 oracle on identical inputs: max abs error <= 2e-2 and max relative
+# error <= 1e-2, the relative error taken over elements with |ref| > REL_FLOOR * max|ref| (below that
+# floor an element is rounding noise of the sums that produced it).
+ABS_TOL = 2e-2
+REL_TOL = 1e-2
+REL_FLOOR = 1e-3
+
+
+def parity_errors(got, ref, rel_floor=REL_FLOOR):
+    got = got.detach().float().cpu()
+    ref = ref.detach().float().cpu()
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    d = (got - ref).abs()
+    floor = rel_floor * ref.abs().max().item()
+    m = ref.abs() > floor
+    rel = (d[m] / ref.abs()[m]).max().item() if m.any() else 0.0
+    return d.max().item(), rel
+
+
+def assert_parity(got, ref, what="", abs_tol=ABS_TOL, rel_tol=REL_TOL, rel_floor=REL_FLOOR):
+    a, r = parity_errors(got, ref, rel_floor)
+    assert a <= abs_tol and r <= rel_tol, f"{what}: max abs {a:.3e} (tol {abs_tol}), max rel {r:.3e} (tol {rel_tol})"
+    return a, r

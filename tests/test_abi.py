@@ -1,0 +1,89 @@
+"""The C-ABI library on a machine without a GPU: it loads, exports every symbol the header declares,
+its structs have the layout the ctypes binding assumes, and argument validation answers before any
+CUDA work."""
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+from triton_b200 import _lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "trinity_b200.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not L.LIB_PATH.exists():
+        from triton_b200.build import build
+        build()
+    return L.load()
+
+
+def test_exports_every_declared_symbol(lib):
+    text = open(HEADER).read()
+    declared = set(re.findall(r"\b(trinity_\w+)\s*\(", text))
+    assert declared == set(L.EXPORTS), declared ^ set(L.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.trinity_abi_version() == L.ABI_VERSION
+
+
+def test_struct_layout_matches_header(tmp_path):
+    structs = {"TrnRmsArgs": L.TrnRmsArgs, "TrnHeadTensor": L.TrnHeadTensor, "TrnProjArgs": L.TrnProjArgs,
+               "TrnAttnArgs": L.TrnAttnArgs, "TrnColStatsArgs": L.TrnColStatsArgs, "TrnTopkArgs": L.TrnTopkArgs,
+               "TrnBlockArgs": L.TrnBlockArgs, "TrnBlockHostArgs": L.TrnBlockHostArgs}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
+    for sname, st in structs.items():
+        lines.append(f'  printf("{sname} %zu\\n", sizeof({sname}));')
+        for fname, _ in st._fields_:
+            lines.append(f'  printf("{sname}.{fname} %zu\\n", offsetof({sname}, {fname}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c11", "-o", str(exe), str(src)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    for line in out.splitlines():
+        key, val = line.split()
+        if "." in key:
+            s, f = key.split(".")
+            assert getattr(structs[s], f).offset == int(val), key
+        else:
+            assert C.sizeof(structs[key]) == int(val), key
+
+
+def test_error_codes_and_messages(lib):
+    for code in range(0, -10, -1):
+        assert lib.trinity_strerror(code).decode() not in ("", "unknown error code")
+    assert lib.trinity_strerror(-99).decode() == "unknown error code"
+    # NULL argument blocks are refused before any CUDA call
+    for fn in (lib.trinity_rmsnorm, lib.trinity_qkv_project, lib.trinity_attention, lib.trinity_attn_colstats,
+               lib.trinity_topk, lib.trinity_attn_block, lib.trinity_attn_block_host):
+        assert fn(None, None) == -1
+    assert lib.trinity_attn_block_workspace(None) == 0
+    a = L.TrnBlockArgs()
+    a.B, a.M, a.Hq = 2, 100, 8
+    # row scales [B*M] + two lse arrays [B,Hq,M], each padded to 256 bytes
+    assert lib.trinity_attn_block_workspace(C.byref(a)) == 1024 + 2 * 6400
+    with pytest.raises(L.TrinityError, match="NULL"):
+        L.check(-1)
+
+
+def test_no_cpu_fallback():
+    import torch
+    from triton_b200 import ops
+    with pytest.raises(ValueError, match="no CPU path"):
+        ops.rmsnorm(torch.randn(4, 64, dtype=torch.bfloat16))
+    with pytest.raises(TypeError):
+        ops._dtype_code(torch.randn(2, 2))
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    monkeypatch.setattr(L, "_lib", None)
+    monkeypatch.setattr(L, "LIB_PATH", tmp_path / "libtrinity_b200.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        L.load()

@@ -1,0 +1,105 @@
+"""Front end and drop-in boundary on CPU: the parser builds the same tree as the reference's
+IrParser.py, the recogniser reports the same TENSOR_PARAMS / BLOCK_PARAMS as the reference's
+TritonCodeGen (fixture tests/golden/ir_metadata.json), and convert_ir_to_triton returns module source
+with the contract the harness relies on (vanilla_llama_benchmark.py:180-256)."""
+import ast as pyast
+import json
+import os
+
+import pytest
+
+from triton_b200.convert_module import convert_ir_to_triton
+from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT, parse_ir_file, resolve_dim
+from triton_b200.ir import ASTNode, IRParser, NodeType
+from triton_b200.recognise import recognise
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+IR_DIR = os.path.join(os.path.dirname(HERE), "triton_b200", "ir_programs")
+META = json.load(open(os.path.join(HERE, "golden", "ir_metadata.json")))
+PROGRAMS = sorted(META)
+
+
+def tree(node):
+    return [node.node_type.value, node.value, [tree(c) for c in node.children]]
+
+
+def read(name):
+    return open(os.path.join(IR_DIR, name + ".txt")).read()
+
+
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_parser_builds_reference_tree(name):
+    assert tree(IRParser().parse(read(name))) == META[name]["ast"]
+
+
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_recogniser_matches_reference_metadata(name):
+    prog = recognise(IRParser().parse(read(name)), SHAPE_DICT)
+    assert prog.variant == name
+    assert prog.tensor_params == META[name]["tensor_params"]
+    assert prog.block_params == META[name]["block_params"]
+    assert prog.n_kernels == META[name]["n_kernels"]
+
+
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_generated_module_contract(name):
+    src = convert_ir_to_triton(read(name), SHAPE_DICT, MODEL_CONFIGS["llama"])
+    mod = pyast.parse(src)
+    assigned = {t.id for n in mod.body if isinstance(n, pyast.Assign) for t in n.targets}
+    assert {"TENSOR_PARAMS", "BLOCK_PARAMS"} <= assigned
+    fwd = next(n for n in mod.body if isinstance(n, pyast.FunctionDef) and n.name == "forward")
+    args = [a.arg for a in fwd.args.args]
+    assert ", ".join(args[:len(META[name]["tensor_params"])]) == ", ".join(META[name]["tensor_params"])
+    # same signature text as the reference's generated forward(): tensors then block_*=16
+    sig = ", ".join(META[name]["tensor_params"] + [f"{b}=16" for b in META[name]["block_params"]])
+    assert sig == META[name]["forward"]
+    assert f"def forward({sig}):" in src
+    # executes on a machine without a GPU (binding happens at the first forward call)
+    ns = {}
+    exec(compile(src, f"<{name}>", "exec"), ns)
+    assert ns["TENSOR_PARAMS"] == META[name]["tensor_params"] and callable(ns["forward"])
+
+
+def test_parser_details():
+    p = IRParser()
+    assert p.tokenize("(a b) ; comment (x\n c,d") == ["(", "a", "b", ")", "c", ",", "d"]
+    n = p.parse("(index fulltile (tile n) (elem k) (const_tile P M) -3 dummy)")
+    assert [c.node_type for c in n.children] == [NodeType.FULLTILE, NodeType.TILE, NodeType.ELEM,
+                                                 NodeType.CONST_TILE, NodeType.NUM, NodeType.DUMMY]
+    assert n.children[4].value == -3
+    multi = p.parse("(load (input Q1,K1, V1) (index fulltile))")
+    assert [c.value for c in multi.children[0].children] == ["Q1", "K1", "V1"]
+    assert p.parse("(tensor P+M)").children[0].value == "P+M"
+    with pytest.raises(ValueError, match="Unknown operation"):
+        p.parse("(frobnicate 1 2)")
+    with pytest.raises(ValueError):
+        p.parse("(seq (load (input X) (index fulltile))")
+    with pytest.raises(ValueError):
+        p.parse("")
+    assert isinstance(n, ASTNode) and repr(p.parse("7")) == "num(7)"
+
+
+def test_recogniser_rejects_foreign_programs():
+    lora = "(store (output O) (* (load (input X) (index fulltile fulltile)) (load (input W) (index fulltile fulltile))) (index fulltile fulltile))"
+    with pytest.raises(ValueError):
+        recognise(IRParser().parse(lora), None)
+    with pytest.raises(ValueError, match="missing from the shape table"):
+        recognise(IRParser().parse(lora), SHAPE_DICT)
+    # an attention program whose result lands in a tensor the operator surface does not know as an output
+    broken = read("vanilla").replace("(output O2)", "(output C)")
+    with pytest.raises(ValueError, match="no output"):
+        recognise(IRParser().parse(broken), SHAPE_DICT)
+    # KeyFormer without its per-key score
+    with pytest.raises(ValueError, match="C_out"):
+        recognise(IRParser().parse(read("keyformer").replace("(output C_out)", "(output C)")), SHAPE_DICT)
+
+
+def test_ir_file_format(tmp_path):
+    f = tmp_path / "cands.txt"
+    one_line = " ".join(l.split(";")[0] for l in read("vanilla").splitlines())
+    f.write_text(f"3: {one_line}\n4: (dummydata)\nnot a candidate\n7: {one_line}\n")
+    got = parse_ir_file(str(f))
+    assert [i for i, _ in got] == [3, 7]
+    assert tree(IRParser().parse(got[0][1])) == META["vanilla"]["ast"]
+    assert parse_ir_file(os.path.join(IR_DIR, "roco.txt"))[0][0] == 0
+    assert resolve_dim("P+M", MODEL_CONFIGS["llama"]) == 1040 and resolve_dim(5, {}) == 5

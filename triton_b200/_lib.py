@@ -56,7 +56,7 @@ class TrnAttnArgs(C.Structure):
         ("B", C.c_int), ("M", C.c_int), ("P", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("D", C.c_int),
         ("dtype", C.c_int), ("causal", C.c_int), ("scale", C.c_float), ("noise_mode", C.c_int), ("tau", C.c_float),
         ("noise", C.c_void_p), ("noise_stride_b", C.c_int64), ("noise_stride_h", C.c_int64),
-        ("noise_stride_i", C.c_int64), ("seed", C.c_uint64),
+        ("noise_stride_i", C.c_int64), ("seed", C.c_uint64), ("single_p", C.c_int),
     ]
 
 
@@ -92,7 +92,7 @@ class TrnBlockArgs(C.Structure):
         ("noise_mode", C.c_int), ("tau", C.c_float), ("noise", C.c_void_p),
         ("noise_stride_b", C.c_int64), ("noise_stride_h", C.c_int64), ("noise_stride_i", C.c_int64),
         ("seed", C.c_uint64),
-        ("sum_p", C.c_void_p), ("sum_p2", C.c_void_p), ("stats_fp32", C.c_int),
+        ("sum_p", C.c_void_p), ("sum_p2", C.c_void_p), ("stats_fp32", C.c_int), ("single_p", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 

@@ -309,6 +309,7 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
   at.scale = a->scale;
   at.noise_mode = TRN_NOISE_NONE;
   at.tau = 1.0f;
+  at.single_p = a->single_p;
   rc = launch_attention(at, st, *ds);
   if (rc != TRN_OK) return rc;
 

@@ -10,7 +10,9 @@
 //              block's q k^T overlaps this block's softmax) and O += P v (fp32 in TMEM)
 //   warps 2-5  one thread per query row: tcgen05.ld S, running max / sum, 2^x, P packed to 16-bit
 //              into swizzled shared memory as the A operand of P v; O is rescaled in TMEM only when
-//              a row's max grew by more than 2^8 since the last rescale
+//              a row's max grew by more than 2^8 since the last rescale.  By default p is split into
+//              two 16-bit parts (hi + lo) and P v is issued for both, so the product carries ~16
+//              mantissa bits of p instead of 8 (bf16) / 11 (fp16).
 // MODE 1 (KeyFormer's second row pass, ref_rms.py:172-174) computes only the log-sum-exp of the
 // perturbed scores (s + g) / tau and skips P, v and O.
 //
@@ -43,7 +45,7 @@ struct AttnParams {
   int* status;
 };
 
-template <int D>
+template <int D, bool SPLIT>
 struct AttnSmem {
   static constexpr int kStages = (D == 128) ? 2 : 4;
   static constexpr int kChunks = D / 64;
@@ -51,7 +53,7 @@ struct AttnSmem {
   static constexpr int kQBytes = kChunks * kChunkBytes;
   static constexpr int kKBytes = kQBytes;
   static constexpr int kVBytes = kQBytes;
-  static constexpr int kPBytes = 2 * kChunkBytes;          // 128 rows x 128 keys
+  static constexpr int kPBytes = (SPLIT ? 4 : 2) * kChunkBytes;   // 128 rows x 128 keys (x2: hi and lo parts)
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = kQBytes;
   static constexpr int kPOff = kKVOff + kStages * (kKBytes + kVBytes);
@@ -59,11 +61,11 @@ struct AttnSmem {
   static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
-template <typename T, int D, int MODE>
+template <typename T, int D, int MODE, bool SPLIT>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
-  using SM = AttnSmem<D>;
+  using SM = AttnSmem<D, SPLIT>;
   constexpr int KS = SM::kStages;
   __shared__ int s_skip;
   if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(p.status);
@@ -214,6 +216,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint64_t bdesc = make_smem_desc(v_s(st) + kk * 2048, SM::kChunkBytes, 1024);
             umma_ss(o_tmem, adesc, bdesc, idesc_pv, (j | kk) != 0 ? 1u : 0u);
           }
+          if (SPLIT) {
+            // low-order part of P (p - hi), same v tile: O += P_lo v
+#pragma unroll
+            for (int kk = 0; kk < BKV / 16; ++kk) {
+              const uint64_t adesc =
+                  make_smem_desc(p_s + (2 + (kk >> 2)) * SM::kChunkBytes + (kk & 3) * 32, 0, 1024);
+              const uint64_t bdesc = make_smem_desc(v_s(st) + kk * 2048, SM::kChunkBytes, 1024);
+              umma_ss(o_tmem, adesc, bdesc, idesc_pv, 1u);
+            }
+          }
           umma_commit(kv_empty(st));
           umma_commit(pv_done);
         }
@@ -324,6 +336,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld32(s_tmem + c * 32, r);
         tmem_wait_ld();
         uint32_t packed[16];
+        uint32_t packed_lo[SPLIT ? 16 : 1];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_run));
@@ -333,14 +346,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (kv0 + c * 32 + i + 1 > limit) p1 = 0.f;
           }
           lsum += p0 + p1;
-          packed[i >> 1] = Io<T>::pack2(p0, p1);
+          const uint32_t hi = Io<T>::pack2(p0, p1);
+          packed[i >> 1] = hi;
+          if (SPLIT) {
+            // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
+            const float2 hf = Io<T>::unpack2(hi);
+            packed_lo[i >> 1] = Io<T>::pack2(p0 - hf.x, p1 - hf.y);
+          }
         }
         uint8_t* chunk = p_gen + (c >> 1) * SM::kChunkBytes;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const uint32_t unit = static_cast<uint32_t>((c & 1) * 4 + u);
-          *reinterpret_cast<uint4*>(chunk + swz128(static_cast<uint32_t>(row), unit)) =
+          const uint32_t off = swz128(static_cast<uint32_t>(row), unit);
+          *reinterpret_cast<uint4*>(chunk + off) =
               make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+          if (SPLIT)
+            *reinterpret_cast<uint4*>(chunk + 2 * SM::kChunkBytes + off) =
+                make_uint4(packed_lo[4 * u], packed_lo[4 * u + 1], packed_lo[4 * u + 2], packed_lo[4 * u + 3]);
         }
       }
       l_run += lsum;
@@ -395,9 +418,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 }
 
-template <typename T, int D, int MODE>
+template <typename T, int D, int MODE, bool SPLIT>
 int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
-  using SM = AttnSmem<D>;
+  using SM = AttnSmem<D, SPLIT>;
   AttnParams p{};
   const int L = a.P + a.M;
   CUtensorMap tm_q, tm_k, tm_v;
@@ -427,7 +450,7 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   p.noise.seed = a.seed;
   p.noise.M = a.M; p.noise.L = L; p.noise.Hq = a.Hq;
   p.status = ds.status;
-  auto kern = attn_fwd_kernel<T, D, MODE>;
+  auto kern = attn_fwd_kernel<T, D, MODE, SPLIT>;
   rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
   if (rc != TRN_OK) return rc;
   const long long grid = static_cast<long long>(p.n_qblocks) * a.B * a.Hq;
@@ -440,8 +463,14 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
 template <typename T>
 int launch_typed(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   const bool pert = a.noise_mode != TRN_NOISE_NONE;
-  if (a.D == 128) return pert ? launch_inst<T, 128, 1>(a, st, ds) : launch_inst<T, 128, 0>(a, st, ds);
-  if (a.D == 64) return pert ? launch_inst<T, 64, 1>(a, st, ds) : launch_inst<T, 64, 0>(a, st, ds);
+  if (a.D == 128) {
+    if (pert) return launch_inst<T, 128, 1, false>(a, st, ds);
+    return a.single_p ? launch_inst<T, 128, 0, false>(a, st, ds) : launch_inst<T, 128, 0, true>(a, st, ds);
+  }
+  if (a.D == 64) {
+    if (pert) return launch_inst<T, 64, 1, false>(a, st, ds);
+    return a.single_p ? launch_inst<T, 64, 0, false>(a, st, ds) : launch_inst<T, 64, 0, true>(a, st, ds);
+  }
   return TRN_E_SHAPE;
 }
 

@@ -127,7 +127,7 @@ def _noise_fields(noise: Optional[torch.Tensor]):
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o: Optional[torch.Tensor], *,
               P: int, causal: bool, scale: float, lse: Optional[torch.Tensor] = None,
               noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
-              seed: int = 0) -> None:
+              seed: int = 0, single_p: bool = False) -> None:
     """o = softmax(scale * q k^T [causal]) v over keys [0, P+M).  All tensors are (b, s, h, d) views."""
     _need_cuda(q, k_cache, v_cache, o, lse, noise)
     B, M, Hq, D = q.shape
@@ -137,7 +137,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o: 
     nptr, nb, nh, ni = _noise_fields(noise)
     a = L.TrnAttnArgs(_head_tensor(q), _head_tensor(k_cache), _head_tensor(v_cache), _head_tensor(o), _ptr(lse),
                       B, M, P, Hq, Hkv, D, _dtype_code(q), int(causal), float(scale), noise_mode, float(tau),
-                      nptr, nb, nh, ni, seed)
+                      nptr, nb, nh, ni, seed, int(single_p))
     L.check(L.load().trinity_attention(C.byref(a), _stream()))
 
 
@@ -186,7 +186,8 @@ class BlockPlan:
                  qk_eps: float = 0.0, gamma_q: Optional[torch.Tensor] = None,
                  gamma_k: Optional[torch.Tensor] = None,
                  noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
-                 seed: int = 0, sum_p: Optional[torch.Tensor] = None, sum_p2: Optional[torch.Tensor] = None):
+                 seed: int = 0, sum_p: Optional[torch.Tensor] = None, sum_p2: Optional[torch.Tensor] = None,
+                 single_p: bool = False):
         _need_cuda(q, k_cache, v_cache, o, x, wq, wk, wv, pre_gamma, gamma_q, gamma_k, noise, sum_p, sum_p2)
         self.variant = variant
         skip = x is None
@@ -218,6 +219,7 @@ class BlockPlan:
         a.seed = seed
         a.sum_p, a.sum_p2 = _ptr(sum_p), _ptr(sum_p2)
         a.stats_fp32 = int(sum_p is not None and sum_p.dtype == torch.float32)
+        a.single_p = int(single_p)
         lib = L.load()
         nbytes = lib.trinity_attn_block_workspace(C.byref(a))
         self._ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)

@@ -1,0 +1,113 @@
+"""Run-time side of a module produced by convert_module.convert_ir_to_triton: binds the harness's
+tensors (by name, in TENSOR_PARAMS order) to one launch plan of the C-ABI library and replays it.
+
+Binding happens on the first call with a given set of tensor addresses (the reference harness makes
+that call before CUDA-graph capture, vanilla_llama_benchmark.py:254-257); later calls with the same
+tensors only launch.  Layouts follow the reference's tensor table (convert_eval_rms.py:62-108):
+X [M,N]; WQ/WK/WV [N, heads*D] used as X @ W; Q / Q_norm [H,M,D]; K_cache / V_cache [H,P+M,D];
+O2 [M,N], O1 [M,H,D] or O [H,M,D]; noise [H,M,P+M]; C_out / C_out1 / C_out2 [H,P+M].
+With a batch constant B > 1 every tensor carries a leading batch dim.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib as L
+from . import ops
+
+
+def _sym(shape: Sequence) -> Tuple:
+    return tuple(shape)
+
+
+class BoundOperator:
+    def __init__(self, spec: Dict):
+        self.variant: str = spec["variant"]
+        self.names = list(spec["tensor_params"])
+        self.shapes = {k: _sym(v) for k, v in spec["shapes"].items()}
+        c = dict(spec["consts"])
+        self.M, self.N, self.D, self.P = c["M"], c["N"], c["D"], c.get("P", 0)
+        self.H = c.get("H", self.N // self.D)
+        self.B = c.get("B", 1)
+        self.Hkv = c.get("HKV", self.H)
+        self.causal = bool(c.get("CAUSAL", 0))
+        self.scale = float(self.D) ** -0.5 if c.get("SCALE_RSQRT_D", 0) else 1.0
+        self.eps = c.get("EPS_E6", 0) * 1e-6
+        self.tau = c.get("TAU_E3", 1500) * 1e-3
+        self.noise_mode = L.TRN_NOISE_GUMBEL if c.get("NOISE_GUMBEL", 0) else L.TRN_NOISE_TENSOR
+        self.seed = c.get("SEED", 0)
+        self.single_p = bool(c.get("SINGLE_P", 0))
+        self._plans: Dict[Tuple[int, ...], object] = {}
+        self._scratch: Dict[str, torch.Tensor] = {}
+
+    # -- layout helpers -------------------------------------------------------------------------
+    def _batched(self, t: torch.Tensor, base_rank: int) -> torch.Tensor:
+        """Adds the batch dim when the tensor was passed without one (B == 1)."""
+        if t.dim() == base_rank:
+            return t.unsqueeze(0)
+        return t
+
+    def _head_view(self, t: torch.Tensor, name: str) -> torch.Tensor:
+        """(b, s, h, d) view of a head-split tensor according to its symbolic shape."""
+        sym = self.shapes.get(name)
+        if sym is None:
+            raise ValueError(f"no shape entry for {name}")
+        sym = tuple(sym[-3:]) if len(sym) >= 3 else tuple(sym)
+        if len(sym) == 2:                     # ('M', 'N'): token-major, heads along columns
+            t2 = self._batched(t, 2)
+            return t2.view(t2.shape[0], t2.shape[1], -1, self.D)
+        t3 = self._batched(t, 3)
+        if sym[0] == "H":                     # ('H', rows, 'D'): head-major
+            return t3.permute(0, 2, 1, 3)
+        return t3                             # ('M', 'H', 'D'): token-major
+
+    def _bind(self, tensors: Sequence[torch.Tensor]):
+        t = dict(zip(self.names, tensors))
+        for name, v in t.items():
+            if not isinstance(v, torch.Tensor) or not v.is_cuda:
+                raise ValueError(f"{name}: triton_b200 operators need CUDA tensors (there is no CPU path)")
+        if self.variant == "rmsnorm":
+            x = t["X"]
+            gamma = t.get("gamma")
+            return ("rms", x, t["X_norm"], gamma, t.get("X2"))
+        B, M, P, H, Hkv, D = self.B, self.M, self.P, self.H, self.Hkv, self.D
+        q_name = "Q_norm" if (self.variant == "qknorm" and "Q_norm" in t) else ("Q" if "Q" in t else None)
+        if q_name is not None:
+            q = self._head_view(t[q_name], q_name)
+        else:
+            if "q" not in self._scratch:
+                self._scratch["q"] = torch.empty(B, M, H, D, dtype=t["X"].dtype, device=t["X"].device)
+            q = self._scratch["q"]
+        o_name = next(n for n in ("O2", "O1", "O") if n in t)
+        kw = dict(B=B, M=M, P=P, Hq=H, Hkv=Hkv, D=D, q=q,
+                  k_cache=self._head_view(t["K_cache"], "K_cache"), v_cache=self._head_view(t["V_cache"], "V_cache"),
+                  o=self._head_view(t[o_name], o_name), x=t["X"].reshape(B * M, self.N), wq=t["WQ"], wk=t["WK"],
+                  wv=t["WV"], causal=self.causal, scale=self.scale, pre_eps=self.eps, qk_eps=self.eps,
+                  pre_gamma=t.get("gamma"), gamma_q=t.get("gamma_q"), gamma_k=t.get("gamma_k"),
+                  single_p=self.single_p)
+        if self.variant == "keyformer":
+            noise = t.get("noise")
+            mode = self.noise_mode if noise is None or self.noise_mode == L.TRN_NOISE_GUMBEL else L.TRN_NOISE_TENSOR
+            nv = None
+            if mode == L.TRN_NOISE_TENSOR:
+                if noise is None:
+                    raise ValueError("KeyFormer needs the noise tensor (or NOISE_GUMBEL=1)")
+                nv = self._batched(noise, 3)
+            kw.update(noise_mode=mode, tau=self.tau, noise=nv, seed=self.seed, sum_p=t["C_out"])
+        elif self.variant == "roco":
+            kw.update(sum_p=t["C_out1"], sum_p2=t["C_out2"])
+        return ("block", ops.BlockPlan(self.variant, **kw))
+
+    def __call__(self, tensors: Sequence[torch.Tensor]) -> None:
+        key = tuple(int(v.data_ptr()) for v in tensors)
+        plan = self._plans.get(key)
+        if plan is None:
+            plan = self._bind(tensors)
+            self._plans[key] = plan
+        if plan[0] == "rms":
+            _, x, y, gamma, x2 = plan
+            ops.rmsnorm(x, gamma, self.eps, out=y)
+        else:
+            plan[1].run()
