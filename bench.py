@@ -1,0 +1,384 @@
+"""Benchmark of the fused attention block on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one call of the whole block (RMSNorm statistics -> QKV projection -> attention
+[-> per-key statistics]) on one batch of synthetic input.  The default workload is the PreNorm Llama3-8B
+bf16 configuration: X[8,2048,4096], RMSNorm eps 1e-5 with gamma, Wq 4096x4096, Wk/Wv 4096x1024, causal
+GQA attention with 32 query / 8 KV heads of 128.  Work per step is counted algorithmically:
+2*T*N*(Hq+2Hkv)*D for the projection plus 4*B*Hq*D*S(S+1)/2 for causal attention (recomputation, masked
+tile waste, exp and norm work are not counted).
+
+Under torchrun (one rank per GPU) every rank runs the same workload on its own data — the block has no
+exchange step — so `value` is the aggregate over ranks from the slowest rank's device time ("weak").
+
+`--impl reference` times the reference's CPU path for the same block (the fp32 PyTorch restatement of
+ref_rms.py in oracle/, all host threads) on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: variant, B, S, N, Hq, Hkv, D, project, topk
+    "prenorm_llama": dict(variant="prenorm", B=8, S=2048, N=4096, Hq=32, Hkv=8, D=128, project=True, topk=0),
+    "vanilla_llama": dict(variant="vanilla", B=1, S=512, N=4096, Hq=32, Hkv=8, D=128, project=True, topk=0),
+    "qknorm_falcon": dict(variant="qknorm", B=4, S=2048, N=4544, Hq=71, Hkv=1, D=64, project=True, topk=0),
+    "keyformer_llama": dict(variant="keyformer", B=4, S=4096, N=0, Hq=32, Hkv=8, D=128, project=False, topk=1024),
+    "roco_falcon": dict(variant="roco", B=2, S=8192, N=0, Hq=71, Hkv=1, D=64, project=False, topk=2048),
+}
+METRIC = "fused attn-block TFLOP/s"
+
+
+def algorithmic_flops(w) -> tuple:
+    T = w["B"] * w["S"]
+    proj = 2 * T * w["N"] * (w["Hq"] + 2 * w["Hkv"]) * w["D"] if w["project"] else 0
+    attn = 4 * w["B"] * w["Hq"] * w["D"] * (w["S"] * (w["S"] + 1) // 2)
+    return proj, attn
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(tflops=d["bf16_tflops"], sustained=d.get("bf16_tflops_sustained"), hbm=d["hbm_gbs"], kind="measured")
+    return dict(tflops=1590.0, sustained=1400.0, hbm=6650.0, kind="fallback")
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks during the timed region (NVML polling thread; read-only)
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost"}
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU reference arm / baseline: the oracle on a bounded sample of the workload
+# ------------------------------------------------------------------------------------------------
+def cpu_sample(w, dt_name="bf16"):
+    """One batch item and `heads` query heads (with their KV heads) of the workload, fp32 on the host."""
+    import torch
+    from oracle import attn_block_ref as O
+    torch.manual_seed(0)
+    grp = w["Hq"] // w["Hkv"]
+    hq = min(w["Hq"], 8 if grp <= 8 else grp)
+    hkv = max(1, hq // grp)
+    S, D, N = w["S"], w["D"], w["N"]
+    if w["project"]:
+        X = torch.randn(S, N)
+        Wq, Wk, Wv = torch.randn(N, hq * D) / N ** 0.5, torch.randn(N, hkv * D) / N ** 0.5, torch.randn(N, hkv * D) / N ** 0.5
+        gamma = 1 + 0.1 * torch.randn(N) if w["variant"] == "prenorm" else None
+        gq = 1 + 0.1 * torch.randn(D) if w["variant"] == "qknorm" else None
+        fn = lambda: O.attn_block(w["variant"], X=X, Wq=Wq, Wk=Wk, Wv=Wv, B=1, M=S, P=0, Hq=hq, Hkv=hkv, D=D, causal=True,
+                                  scale=D ** -0.5, pre_eps=1e-5, pre_gamma=gamma, qk_eps=1e-5, gamma_q=gq, gamma_k=gq)
+        proj = 2 * S * N * (hq + 2 * hkv) * D
+    else:
+        hq = min(hq, 2 * grp) if w["S"] >= 8192 else hq
+        hkv = max(1, hq // grp)
+        Q, K, V = torch.randn(1, hq, S, D), torch.randn(1, hkv, S, D), torch.randn(1, hkv, S, D)
+        noise = O.gumbel_noise(0, 1, hq, S, S) if w["variant"] == "keyformer" else None
+        fn = lambda: O.attn_block(w["variant"], Q=Q, K=K, V=V, B=1, M=S, P=0, Hq=hq, Hkv=hkv, D=D, causal=True,
+                                  scale=D ** -0.5, tau=1.0, noise=noise)
+        proj = 0
+    flops = proj + 4 * hq * D * (S * (S + 1) // 2)
+    desc = f"1 of {w['B']} batch items x {hq} of {w['Hq']} query heads ({hkv} kv), fp32 torch on host cores"
+    return fn, flops, desc
+
+
+def time_cpu(fn, steps, warmup):
+    import torch
+    torch.set_num_threads(os.cpu_count() or 1)
+    with torch.no_grad():
+        for _ in range(warmup):
+            fn()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()
+        return (time.perf_counter() - t0) / steps
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    fn, flops, desc = cpu_sample(w)
+    # bounded: at most ~120 s of CPU work whatever K is
+    t1 = time_cpu(fn, 1, 1)
+    steps = max(1, min(args.steps, int(120 / max(t1, 1e-3))))
+    warm = min(args.warmup, 2)
+    sec = time_cpu(fn, steps, warm)
+    value = flops / sec / 1e12
+    full = sum(algorithmic_flops(w))
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warm, "ms_per_step": sec * 1e3 * full / flops, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, **{k: w[k] for k in ("variant", "B", "S", "N", "Hq", "Hkv", "D")},
+                       "note": "ms_per_step is the sample's time scaled to the whole workload by algorithmic flops"},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args, w):
+    import torch
+    import torch.distributed as dist
+    from triton_b200 import _lib as L
+    from triton_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the kernels have no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    dt = torch.bfloat16
+    B, S, N, Hq, Hkv, D = (w[k] for k in ("B", "S", "N", "Hq", "Hkv", "D"))
+    variant = w["variant"]
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+
+    q = torch.empty(B, S, Hq, D, device=dev, dtype=dt)
+    kc = torch.empty(B, Hkv, S, D, device=dev, dtype=dt)
+    vc = torch.empty(B, Hkv, S, D, device=dev, dtype=dt)
+    o = torch.empty(B, S, Hq, D, device=dev, dtype=dt)
+    kw = {}
+    x = None
+    if w["project"]:
+        x = rnd(B * S, N).to(dt)
+        kw = dict(x=x, wq=(rnd(N, Hq * D) / N ** 0.5).to(dt), wk=(rnd(N, Hkv * D) / N ** 0.5).to(dt),
+                  wv=(rnd(N, Hkv * D) / N ** 0.5).to(dt), pre_eps=1e-5, qk_eps=1e-5)
+        if variant == "prenorm":
+            kw["pre_gamma"] = (1 + 0.1 * rnd(N)).to(dt)
+        if variant == "qknorm":
+            kw["gamma_q"], kw["gamma_k"] = (1 + 0.1 * rnd(D)).to(dt), (1 + 0.1 * rnd(D)).to(dt)
+    else:
+        q.copy_(rnd(B, S, Hq, D)); kc.copy_(rnd(B, Hkv, S, D)); vc.copy_(rnd(B, Hkv, S, D))
+    sp = torch.empty(B, Hq, S, device=dev) if variant in ("keyformer", "roco") else None
+    sp2 = torch.empty(B, Hq, S, device=dev) if variant == "roco" else None
+    idx = torch.empty(B, Hq, w["topk"], device=dev, dtype=torch.int32) if w["topk"] else None
+    plan = ops.BlockPlan(variant, B=B, M=S, P=0, Hq=Hq, Hkv=Hkv, D=D, q=ops.as_bshd(q, "bshd"),
+                         k_cache=ops.as_bshd(kc, "bhsd"), v_cache=ops.as_bshd(vc, "bhsd"), o=ops.as_bshd(o, "bshd"),
+                         causal=True, scale=D ** -0.5, noise_mode=L.TRN_NOISE_GUMBEL if variant == "keyformer" else 0,
+                         tau=1.0, seed=0, sum_p=sp, sum_p2=sp2, **kw)
+
+    def step():
+        plan.run()
+        if idx is not None:
+            ops.topk_keys(sp, w["topk"], out=idx)
+
+    launches_per_step = {"vanilla": 2, "prenorm": 3, "qknorm": 2, "keyformer": 3, "roco": 2}[variant]
+    if not w["project"]:
+        launches_per_step -= 1
+    if idx is not None:
+        launches_per_step += 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    if L.kernel_status() != 0:
+        raise RuntimeError(f"kernel status {L.kernel_status()} after warm-up")
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+
+    # ---- per-kernel device times over the same data (events around each launch, same stream)
+    kern_us = {}
+    if rank == 0 and w["project"]:
+        rows = B * S
+        rstd = torch.empty(rows, device=dev)
+        xn = torch.empty_like(x) if variant == "prenorm" else None
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+        for ev in evs:
+            ev[0].record(stream)
+            xin = x
+            if variant == "prenorm":
+                ops.rmsnorm(x, kw["pre_gamma"], 1e-5, out=xn)
+                xin = xn
+            ev[1].record(stream)
+            ops.qkv_project(xin, kw["wq"], kw["wk"], kw["wv"], q=ops.as_bshd(q, "bshd"), k_cache=ops.as_bshd(kc, "bhsd"),
+                            v_cache=ops.as_bshd(vc, "bhsd"), B=B, M=S, P=0, Hq=Hq, Hkv=Hkv, D=D,
+                            qk_norm=variant == "qknorm", qk_eps=1e-5, gamma_q=kw.get("gamma_q"), gamma_k=kw.get("gamma_k"))
+            ev[2].record(stream)
+            ops.attention(ops.as_bshd(q, "bshd"), ops.as_bshd(kc, "bhsd"), ops.as_bshd(vc, "bhsd"), ops.as_bshd(o, "bshd"),
+                          P=0, causal=True, scale=D ** -0.5)
+            ev[3].record(stream)
+        torch.cuda.synchronize()
+        for i, name in enumerate(("rmsnorm", "qkv_gemm", "attention")):
+            kern_us[name] = sum(ev[i].elapsed_time(ev[i + 1]) for ev in evs) / len(evs) * 1e3
+
+    # ---- end to end through the C ABI with host buffers (H2D of X, D2H of O inside the timed region)
+    e2e = None
+    if w["project"]:
+        xh = torch.empty(B * S, N, dtype=dt).pin_memory()
+        xh.copy_(x.cpu())
+        oh = torch.empty(B, S, Hq, D, dtype=dt).pin_memory()
+        ha = L.TrnBlockHostArgs()
+        C.memmove(C.byref(ha.dev), C.byref(plan.args), C.sizeof(L.TrnBlockArgs))
+        ha.x_host, ha.o_host = xh.data_ptr(), oh.data_ptr()
+        ha.x_bytes, ha.o_bytes = xh.numel() * 2, oh.numel() * 2
+        lib = L.load()
+        sraw = stream.cuda_stream
+        for _ in range(2):
+            L.check(lib.trinity_attn_block_host(C.byref(ha), sraw))
+        barrier()
+        n_e2e = max(3, min(args.steps, 20))
+        t0 = time.perf_counter()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(n_e2e):
+            L.check(lib.trinity_attn_block_host(C.byref(ha), sraw))
+        f1.record(stream)
+        barrier()
+        e2e_ms = f0.elapsed_time(f1) / n_e2e
+        e2e = (e2e_ms, ha.x_bytes, ha.o_bytes, float(oh.float().abs().mean()))
+    clocks = sampler.stop()
+
+    ms_step = ms_total / args.steps
+    if world > 1:
+        t = torch.tensor([ms_step, e2e[0] if e2e else 0.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t[0])
+        if e2e:
+            e2e = (float(t[1]),) + e2e[1:]
+    status = L.kernel_status()
+    if status != 0:
+        raise RuntimeError(f"kernel status {status}")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+
+    proj_f, attn_f = algorithmic_flops(w)
+    flops = proj_f + attn_f
+    peaks = measured_peaks()
+    value = world * flops / (ms_step * 1e-3) / 1e12
+    line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "variant": variant, "B": B, "S": S, "N": N, "Hq": Hq, "Hkv": Hkv, "D": D,
+                       "causal": True, "parallelism": f"replicas x{world} (no data-path collective)",
+                       "l2": "per-step working set (X, W, Q, K/V, O ~ 0.57 GB) is larger than the 126 MB L2",
+                       "flops_per_step": flops},
+            "us_per_call": ms_step * 1e3,
+            "frac_of_bf16_peak": value / world / peaks["tflops"], "peak_kind": peaks["kind"],
+            "clocks": clocks, "gpu_launches": launches_per_step * args.steps}
+    if e2e:
+        line["e2e"] = {"value": world * flops / (e2e[0] * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e[0],
+                       "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2],
+                       "api": "trinity_attn_block_host (pinned host X in, O out; weights resident)"}
+    else:
+        line["e2e"] = None
+    if kern_us:
+        line["kernels_us"] = kern_us
+        ach = proj_f / (kern_us["qkv_gemm"] * 1e-6) / 1e12
+        line["roofline"] = {"kernel": "qkv_gemm_kernel", "bound": "tensor", "achieved": ach, "peak": peaks["tflops"],
+                            "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "peak_source": peaks["kind"] + " burst",
+                            "traffic": TRAFFIC_BYTES.get(args.workload)}
+        line["attention_tflops"] = attn_f / (kern_us["attention"] * 1e-6) / 1e12
+    if world == 1 and not args.no_cpu:
+        fn, cflops, desc = cpu_sample(w)
+        sec = time_cpu(fn, 2, 1)
+        line["cpu_baseline"] = {"value": cflops / sec / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                                "sample": desc}
+    print(json.dumps(line))
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one qkv_gemm_kernel launch, from the ncu capture
+# summarised under profiles/ (None until captured for that workload)
+TRAFFIC_BYTES = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="prenorm_llama")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

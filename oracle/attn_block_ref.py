@@ -94,7 +94,8 @@ def gumbel_noise(seed: int, B: int, Hq: int, M: int, L: int, b0: int = 0, b1: Op
 def project(variant: str, X: torch.Tensor, Wq: torch.Tensor, Wk: torch.Tensor, Wv: torch.Tensor, *,
             B: int, M: int, Hq: int, Hkv: int, D: int, pre_eps: float = 0.0,
             pre_gamma: Optional[torch.Tensor] = None, qk_eps: float = 0.0,
-            gamma_q: Optional[torch.Tensor] = None, gamma_k: Optional[torch.Tensor] = None):
+            gamma_q: Optional[torch.Tensor] = None, gamma_k: Optional[torch.Tensor] = None,
+            round_x_norm: Optional[torch.dtype] = None):
     """q [B,Hq,M,D], k, v [B,Hkv,M,D] in fp32, following ref_rms.py:47-56 (+102-103, +217-220)."""
     Xf = X.float().reshape(B, M, -1)
     if variant == "prenorm":
@@ -102,6 +103,8 @@ def project(variant: str, X: torch.Tensor, Wq: torch.Tensor, Wk: torch.Tensor, W
         Xf = Xf * torch.rsqrt(variance + pre_eps)            # ref_rms.py:103
         if pre_gamma is not None:
             Xf = Xf * pre_gamma.float()
+        if round_x_norm is not None:                         # X_norm stored as a 16-bit tensor
+            Xf = Xf.to(round_x_norm).float()
     q = torch.matmul(Xf, Wq.float())                         # ref_rms.py:47
     k = torch.matmul(Xf, Wk.float())
     v = torch.matmul(Xf, Wv.float())
@@ -158,18 +161,21 @@ def attn_block(variant: str, *, X: Optional[torch.Tensor] = None, Wq=None, Wk=No
                cache_V: Optional[torch.Tensor] = None, B: int = 1, M: int, P: int = 0, Hq: int, Hkv: int, D: int,
                causal: bool = False, scale: float = 1.0, pre_eps: float = 0.0, pre_gamma=None,
                qk_eps: float = 0.0, gamma_q=None, gamma_k=None, tau: float = 1.5, noise=None,
-               round_to: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
+               round_to: Optional[torch.dtype] = None,
+               round_x_norm: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
     """Whole block.  X [B*M, N] with weights, or Q [B,Hq,M,D], K, V [B,Hkv,M,D] given directly.
     cache_K / cache_V: [B,Hkv,>=P,D] prefix (rows [0,P) are used, as ref_rms.py:72-73).
 
-    round_to: if set, q / k / v are rounded to that dtype after projection (what a kernel that stores
-    them in 16 bits does) before attention, so that index-exact comparisons (top-k) see the same
-    inputs; parity of `out` is always judged against round_to=None as well.
+    round_to: if set, q / k / v are rounded to that dtype after projection before attention — the
+    operator surface defines Q, K_cache and V_cache as 16-bit tensors (convert_eval_rms.py:71-84), and
+    the reference's own fp16 path rounds them there too.  round_x_norm does the same for X_norm
+    (convert_eval_rms.py:65) where an implementation materialises it.
     """
     assert variant in VARIANTS
     if X is not None:
         q, k, v = project(variant, X, Wq, Wk, Wv, B=B, M=M, Hq=Hq, Hkv=Hkv, D=D, pre_eps=pre_eps,
-                          pre_gamma=pre_gamma, qk_eps=qk_eps, gamma_q=gamma_q, gamma_k=gamma_k)
+                          pre_gamma=pre_gamma, qk_eps=qk_eps, gamma_q=gamma_q, gamma_k=gamma_k,
+                          round_x_norm=round_x_norm)
     else:
         q, k, v = Q.float(), K.float(), V.float()
     if round_to is not None:

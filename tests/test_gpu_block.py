@@ -1,0 +1,183 @@
+"""Whole attention blocks through trinity_attn_block (the unit the reference's generated forward()
+computes) against the CPU oracle and against outputs of the reference's own classes (golden fixture).
+
+Two comparisons per case:
+  * strict: the oracle evaluated with the same 16-bit storage points as the operator surface (Q,
+    K_cache, V_cache — and X_norm where the block materialises it — are 16-bit tensors in the reference's
+    tensor table, convert_eval_rms.py:62-108): abs <= 2e-2, rel <= 1e-2 above 1e-3 of max|ref|;
+  * against the pure fp32 oracle: abs <= 2e-2, and rel <= 1e-2 above 1e-1 of max|ref| — rounding q, k, v
+    to 16 bits perturbs every score by ~2^-9 relative, which no 16-bit path avoids.
+"""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_parity
+from gpu_util import block_inputs, run_block
+from oracle import attn_block_ref as O
+from triton_b200 import _lib as L
+from triton_b200 import ops
+from triton_b200.convert_module import convert_ir_to_triton
+from triton_b200.harness import IR_DIR, MODEL_CONFIGS, SHAPE_DICT, AttnBlockBenchmark
+
+pytestmark = pytest.mark.gpu
+BF, HF = torch.bfloat16, torch.float16
+VARIANTS = ("vanilla", "prenorm", "qknorm", "keyformer", "roco")
+REL_FLOOR_FP32 = 1e-1
+
+
+def _oracle(variant, t, dims, causal, scale, eps, tau, noise, round_to=None, round_x_norm=None):
+    B, M, P, N, Hq, Hkv, D = dims
+    return O.attn_block(variant, X=t["X"], Wq=t["WQ"], Wk=t["WK"], Wv=t["WV"], cache_K=t["K_cache"],
+                        cache_V=t["V_cache"], B=B, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, causal=causal, scale=scale,
+                        pre_eps=eps, pre_gamma=t["pre_gamma"], qk_eps=eps, gamma_q=t["gamma_q"], gamma_k=t["gamma_k"],
+                        tau=tau, noise=noise, round_to=round_to, round_x_norm=round_x_norm)
+
+
+def _check_block(variant, dims, dt, causal, scale, eps, gamma, ref_native, noise_mode=L.TRN_NOISE_TENSOR, seed=4):
+    B, M, P, N, Hq, Hkv, D = dims
+    t = block_inputs(seed, B, M, P, N, Hq, Hkv, D, dt, ref_native=ref_native, variant=variant, gamma=gamma,
+                     noise_mode=noise_mode)
+    tau = 1.5
+    noise = t["noise"]
+    if variant == "keyformer" and noise_mode == L.TRN_NOISE_GUMBEL:
+        noise = O.gumbel_noise(11, B, Hq, M, P + M)
+    got = run_block(variant, t, B=B, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, causal=causal, scale=scale, eps=eps, tau=tau,
+                    noise_mode=noise_mode, seed=11)
+    strict = _oracle(variant, t, dims, causal, scale, eps, tau, noise, round_to=dt,
+                     round_x_norm=dt if t["pre_gamma"] is not None else None)
+    pure = _oracle(variant, t, dims, causal, scale, eps, tau, noise)
+    assert_parity(got["out"], strict["out_bmhd"], f"{variant} out (16-bit storage points)")
+    assert_parity(got["out"], pure["out_bmhd"], f"{variant} out (fp32 oracle)", rel_floor=REL_FLOOR_FP32)
+    # projected tensors as stored
+    assert_parity(got["q"], pure["q"].transpose(1, 2), "q")
+    assert_parity(got["k_cache"], pure["k_all"], "k_cache")
+    assert_parity(got["v_cache"], pure["v_all"], "v_cache")
+    if variant in ("keyformer", "roco"):
+        assert_parity(got["sum_p"], strict["sum_p"], "sum_p", abs_tol=2e-2 * max(1.0, M / 16), rel_tol=1e-2)
+        assert_parity(got["sum_p"], pure["sum_p"], "sum_p (fp32 oracle)", abs_tol=2e-2 * max(1.0, M / 16),
+                      rel_tol=1e-2, rel_floor=REL_FLOOR_FP32)
+    if variant == "roco":
+        assert_parity(got["sum_p2"], strict["sum_p2"], "sum_p2", abs_tol=2e-2 * max(1.0, M / 16), rel_tol=2e-2)
+    return got, strict, pure
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_block_reference_semantics_small(variant):
+    # the reference's semantics: non-causal, unscaled, no eps / gamma, tau 1.5, MHA, its input recipe
+    _check_block(variant, (1, 16, 48, 256, 4, 4, 64), HF, False, 1.0, 0.0, False, True)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_block_generalised_small(variant):
+    # batch, GQA, causal, scaled, eps + gamma, ragged M
+    _check_block(variant, (2, 200, 0, 512, 8, 2, 64), BF, True, 0.125, 1e-5, True, False)
+    _check_block(variant, (1, 130, 24, 256, 4, 2, 128), BF, True, 128 ** -0.5, 1e-5, True, False,
+                 noise_mode=L.TRN_NOISE_GUMBEL)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("model", ("llama", "falcon"))
+def test_block_reference_native_shapes(variant, model):
+    c = MODEL_CONFIGS[model]
+    _check_block(variant, (1, c["M"], c["P"], c["N"], c["H"], c["H"], c["D"]), HF, False, 1.0, 0.0, False, True)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_block_against_reference_class_outputs(variant):
+    """Inputs and outputs of the reference's own classes (tests/golden/golden_small.npz, fp32) — the kernels
+    see the inputs rounded to fp16, as the reference's harness feeds them (convert_eval_rms.py:24)."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden_small.npz"))
+    M, N, D, H, P = (int(v) for v in g["dims"])
+    t = {k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("in_")}
+    tin = dict(X=t["X"].half(), WQ=t["WQ"].half(), WK=t["WK"].half(), WV=t["WV"].half(),
+               K_cache=t["K_cache"].half().unsqueeze(0), V_cache=t["V_cache"].half().unsqueeze(0),
+               pre_gamma=None, gamma_q=None, gamma_k=None,
+               noise=t["noise"].half().unsqueeze(0) if variant == "keyformer" else None)
+    got = run_block(variant, tin, B=1, M=M, P=P, Hq=H, Hkv=H, D=D, causal=False, scale=1.0, tau=1.5)
+    # the reference returns the head-major result viewed as [M, H*D] (ref_rms.py:80-81)
+    ref_out = torch.from_numpy(g[f"{variant}_out"]).view(H, M, D).permute(1, 0, 2)
+    assert_parity(got["out"][0], ref_out, f"{variant} vs reference class", rel_floor=REL_FLOOR_FP32)
+    if variant == "keyformer":
+        assert_parity(got["sum_p"][0], torch.from_numpy(g["keyformer_perturb_out"]).sum(1), "C_out",
+                      rel_floor=REL_FLOOR_FP32)
+    if variant == "roco":
+        assert_parity(got["sum_p"][0], torch.from_numpy(g["roco_sum_p"]), "C_out1", rel_floor=REL_FLOOR_FP32)
+        assert_parity(got["sum_p2"][0], torch.from_numpy(g["roco_sum_p2"]), "C_out2", rel_floor=REL_FLOOR_FP32, rel_tol=2e-2)
+
+
+def _load_generated(src, name):
+    import tempfile
+    with tempfile.NamedTemporaryFile("w", suffix=".py", delete=False) as f:
+        f.write(src)
+    spec = importlib.util.spec_from_file_location(name, f.name)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    os.unlink(f.name)
+    return mod
+
+
+@pytest.mark.parametrize("variant", VARIANTS + ("rmsnorm",))
+def test_generated_forward_in_place_and_graph_capturable(variant):
+    """The drop-in path end to end: IR text -> convert_ir_to_triton -> module.forward(*tensors) with the
+    reference's tensor names, layouts and dtypes, replayed from a CUDA graph as the reference's harness
+    does (vanilla_llama_benchmark.py:263-285)."""
+    consts = {"M": 16, "N": 256, "D": 64, "H": 4, "P": 48}
+    src = convert_ir_to_triton(open(IR_DIR / f"{variant}.txt").read(), SHAPE_DICT, consts)
+    mod = _load_generated(src, f"gen_{variant}")
+    bench = AttnBlockBenchmark(consts, seed=42)
+    bench.create_test_tensors(mod.TENSOR_PARAMS)
+    T = bench.tensors
+    args = [T[p] for p in mod.TENSOR_PARAMS]
+    host = {k: v.detach().cpu().clone() for k, v in T.items()}
+    assert mod.forward(*args) is None
+    torch.cuda.synchronize()
+    if variant == "rmsnorm":
+        assert_parity(T["X_norm"], O.rmsnorm(host["X"]), "X_norm")
+    else:
+        r = O.attn_block(variant, X=host["X"], Wq=host["WQ"], Wk=host["WK"], Wv=host["WV"],
+                         cache_K=host["K_cache"].unsqueeze(0), cache_V=host["V_cache"].unsqueeze(0), B=1, M=16, P=48,
+                         Hq=4, Hkv=4, D=64, noise=host["noise"].unsqueeze(0) if "noise" in host else None,
+                         round_to=HF, round_x_norm=None)
+        assert_parity(T["O2"].view(16, 4, 64), r["out_bmhd"][0], "O2")
+        assert_parity(T["K_cache"][:, 48:], r["k_all"][0, :, 48:], "cache append")
+        assert torch.equal(T["K_cache"][:, :48].cpu(), host["K_cache"][:, :48])
+        if variant == "keyformer":
+            assert_parity(T["C_out"], r["sum_p"][0], "C_out")
+        if variant == "roco":
+            assert_parity(T["C_out1"], r["sum_p"][0], "C_out1")
+            assert_parity(T["C_out2"], r["sum_p2"][0], "C_out2", rel_tol=2e-2)
+    # positional block sizes (convert_eval_rms.py:275-291) and keyword block sizes (rms_benchmark.py:246-263)
+    mod.forward(*args, *([32] * len(mod.BLOCK_PARAMS)))
+    mod.forward(*args, **{b: 64 for b in mod.BLOCK_PARAMS})
+    out_name = "X_norm" if variant == "rmsnorm" else "O2"
+    want = T[out_name].clone()
+    ms = bench.benchmark_kernel(mod, warmup_runs=2, benchmark_runs=5)      # zeroes outputs, captures, replays
+    assert ms > 0 and torch.equal(T[out_name], want)
+    bench.cleanup()
+
+
+def test_harness_records_errors_instead_of_raising():
+    bench = AttnBlockBenchmark({"M": 16, "N": 256, "D": 64, "H": 4, "P": 48})
+    r = bench.run_single_benchmark(5, "(frobnicate X)")
+    assert r.error is not None and r.execution_time == float("inf") and r.ir_id == 5
+    good = bench.run_single_benchmark(0, open(IR_DIR / "vanilla.txt").read())
+    assert good.error is None and good.execution_time > 0
+    bench.cleanup()
+
+
+def test_block_argument_validation():
+    t = block_inputs(0, 1, 16, 0, 128, 2, 2, 64, BF)
+    with pytest.raises(ValueError, match="weight shapes"):
+        bad = dict(t)
+        bad["WK"] = t["WK"][:, :64].contiguous()
+        run_block("vanilla", bad, B=1, M=16, P=0, Hq=2, Hkv=2, D=64, causal=False, scale=1.0)
+    # KeyFormer without noise and without the Gumbel generator
+    with pytest.raises(L.TrinityError):
+        run_block("keyformer", t, B=1, M=16, P=0, Hq=2, Hkv=2, D=64, causal=False, scale=1.0, noise_mode=L.TRN_NOISE_TENSOR)
+    assert L.kernel_status() == 0

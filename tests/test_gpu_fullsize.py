@@ -1,0 +1,113 @@
+"""The benchmark configurations at full size.  The fp32 oracle cannot materialise [heads, S, S] scores for
+these shapes in seconds, so parity is checked (a) exactly as in the small tests on a few (batch, head)
+slices evaluated by the oracle, and (b) through size-independent properties of attention:
+rows of probabilities sum to one (V = 1 gives O = 1; per-key sums add up to the number of queries),
+the first causal row returns v_0, and O is linear in V."""
+import math
+
+import pytest
+import torch
+
+from conftest import assert_parity
+from oracle import attn_block_ref as O
+from triton_b200 import _lib as L
+from triton_b200 import ops
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+CONFIGS = {
+    # name: B, S, Hq, Hkv, D, variant, topk
+    "keyformer_llama": (4, 4096, 32, 8, 128, "keyformer", 1024),
+    "roco_falcon": (2, 8192, 71, 1, 64, "roco", 2048),
+}
+
+
+def _run(q, k, v, o, scale, lse=None):
+    ops.attention(ops.as_bshd(q, "bshd"), ops.as_bshd(k, "bshd"), ops.as_bshd(v, "bshd"), ops.as_bshd(o, "bshd"),
+                  P=0, causal=True, scale=scale, lse=lse)
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_full_size_properties_and_sampled_parity(name):
+    B, S, Hq, Hkv, D, variant, topk = CONFIGS[name]
+    scale = D ** -0.5
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.randn(B, S, Hq, D, device="cuda", generator=g).to(BF)
+    k = torch.randn(B, S, Hkv, D, device="cuda", generator=g).to(BF)
+    v = torch.randn(B, S, Hkv, D, device="cuda", generator=g).to(BF)
+    o = torch.empty(B, S, Hq, D, device="cuda", dtype=BF)
+    lse = torch.empty(B, Hq, S, device="cuda")
+    _run(q, k, v, o, scale, lse)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0 and not torch.isnan(o).any()
+    # first causal row sees only key 0
+    grp = Hq // Hkv
+    assert torch.equal(o[:, 0], v[:, 0].repeat_interleave(grp, dim=1))
+    # V = 1  =>  O = 1 (probabilities sum to one); hi + lo parts of p make this tight
+    ones = torch.ones_like(v)
+    o1 = torch.empty_like(o)
+    _run(q, k, ones, o1, scale)
+    assert (o1.float() - 1).abs().max().item() <= 4e-3
+    # linearity in V
+    v2 = torch.randn(B, S, Hkv, D, device="cuda", generator=g).to(BF)
+    o2, o12 = torch.empty_like(o), torch.empty_like(o)
+    _run(q, k, v2, o2, scale)
+    _run(q, k, (v.float() + v2.float()).to(BF), o12, scale)
+    assert (o12.float() - (o.float() + o2.float())).abs().max().item() <= 6e-2
+    # per-key statistics: fixed-order sums, total = number of queries
+    sp = torch.empty(B, Hq, S, device="cuda")
+    sp2 = torch.empty(B, Hq, S, device="cuda") if variant == "roco" else None
+    if variant == "roco":
+        ops.attn_colstats(ops.as_bshd(q, "bshd"), ops.as_bshd(k, "bshd"), lse, sp, sp2, P=0, causal=True, scale=scale)
+    else:
+        lse_p = torch.empty_like(lse)
+        ops.attention(ops.as_bshd(q, "bshd"), ops.as_bshd(k, "bshd"), ops.as_bshd(v, "bshd"), None, P=0, causal=True,
+                      scale=scale, lse=lse_p, noise_mode=L.TRN_NOISE_GUMBEL, tau=1.0, seed=0)
+        ops.attn_colstats(ops.as_bshd(q, "bshd"), ops.as_bshd(k, "bshd"), lse_p, sp, None, P=0, causal=True,
+                          scale=scale, noise_mode=L.TRN_NOISE_GUMBEL, tau=1.0, seed=0)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    assert (sp.sum(-1) - S).abs().max().item() <= 1e-3 * S
+    idx = ops.topk_keys(sp, topk)
+    torch.cuda.synchronize()
+    assert torch.equal(idx.cpu(), O.topk_keys(sp.cpu(), topk))
+    # sampled (batch, head) slices against the oracle
+    for b, h in ((0, 0), (B - 1, Hq - 1)):
+        kv = h // grp
+        noise = O.gumbel_noise(0, B, Hq, S, S, b0=b, b1=b + 1, h0=h, h1=h + 1) if variant == "keyformer" else None
+        r = O.attend(q[b:b + 1, :, h:h + 1].float().cpu().transpose(1, 2), k[b:b + 1, :, kv:kv + 1].float().cpu().transpose(1, 2),
+                     v[b:b + 1, :, kv:kv + 1].float().cpu().transpose(1, 2), P=0, causal=True, scale=scale,
+                     variant=variant, tau=1.0, noise=noise)
+        assert_parity(o[b, :, h], r["out"][0, 0], f"{name} out[{b},{h}]")
+        assert_parity(sp[b, h], r["sum_p"][0, 0], f"{name} sum_p[{b},{h}]", abs_tol=1e-2, rel_tol=1e-3)
+        want = O.topk_keys(r["sum_p"][0, 0], topk)
+        if not torch.equal(idx[b, h].cpu(), want):
+            # only swaps between scores closer than the fp32 noise of a 4096- / 8192-term sum are tolerated
+            srt = torch.sort(r["sum_p"][0, 0], descending=True)
+            pos = (idx[b, h].cpu() != want).nonzero()[0].item()
+            gap = (srt.values[pos] - srt.values[min(pos + 1, S - 1)]).item()
+            assert gap <= 1e-5 * srt.values[0].item(), f"top-k differs at rank {pos}, score gap {gap:.3e}"
+            assert set(idx[b, h].cpu().tolist()) ^ set(want.tolist()) <= set(srt.indices[max(0, topk - 4):topk + 4].tolist())
+        if variant == "roco":
+            assert_parity(sp2[b, h], r["sum_p2"][0, 0], f"{name} sum_p2", abs_tol=1e-2, rel_tol=1e-3)
+
+
+def test_prenorm_config_sampled_parity():
+    """PreNorm Llama3-8B block at full size (X[8,2048,4096]): whole block on the GPU, oracle on one batch
+    item and two kv groups."""
+    from gpu_util import block_inputs, run_block
+    B, S, N, Hq, Hkv, D = 8, 2048, 4096, 32, 8, 128
+    t = block_inputs(0, B, S, 0, N, Hq, Hkv, D, BF, variant="prenorm", gamma=True)
+    got = run_block("prenorm", t, B=B, M=S, P=0, Hq=Hq, Hkv=Hkv, D=D, causal=True, scale=D ** -0.5, eps=1e-5)
+    b = B - 1
+    heads = slice(0, 4)            # kv group 0
+    ts = dict(t)
+    r = O.attn_block("prenorm", X=t["X"].view(B, S, N)[b], Wq=t["WQ"][:, :4 * D], Wk=t["WK"][:, :D], Wv=t["WV"][:, :D],
+                     B=1, M=S, P=0, Hq=4, Hkv=1, D=D, causal=True, scale=D ** -0.5, pre_eps=1e-5,
+                     pre_gamma=t["pre_gamma"], round_to=BF, round_x_norm=BF)
+    assert_parity(got["out"][b, :, heads], r["out_bmhd"][0], "prenorm cfg out (16-bit storage points)")
+    pure = O.attn_block("prenorm", X=t["X"].view(B, S, N)[b], Wq=t["WQ"][:, :4 * D], Wk=t["WK"][:, :D], Wv=t["WV"][:, :D],
+                        B=1, M=S, P=0, Hq=4, Hkv=1, D=D, causal=True, scale=D ** -0.5, pre_eps=1e-5,
+                        pre_gamma=t["pre_gamma"])
+    assert_parity(got["out"][b, :, heads], pure["out_bmhd"][0], "prenorm cfg out (fp32 oracle)", rel_floor=1e-1)

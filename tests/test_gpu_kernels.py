@@ -1,0 +1,250 @@
+"""Parity of the individual sm_100a kernels (through the C ABI) against the fp32 CPU oracle on the same
+seeded inputs: RMSNorm, QKV projection with its fused epilogues, the attention core, the per-key
+statistics and top-k.  Tolerances: see tests/conftest.py (abs 2e-2, rel 1e-2 above 1e-3 of max|ref|)."""
+import math
+
+import pytest
+import torch
+
+from conftest import assert_parity, parity_errors
+from oracle import attn_block_ref as O
+from triton_b200 import _lib as L
+from triton_b200 import ops
+
+pytestmark = pytest.mark.gpu
+BF, HF = torch.bfloat16, torch.float16
+
+
+@pytest.mark.parametrize("dt", (BF, HF))
+@pytest.mark.parametrize("rows,cols", ((1, 8), (5, 64), (16, 4096), (33, 4544), (7, 1024), (3, 8192), (2, 20000)))
+@pytest.mark.parametrize("use_gamma", (False, True))
+def test_rmsnorm(dt, rows, cols, use_gamma):
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols).to(dt)
+    g = (1 + 0.1 * torch.randn(cols)).to(dt) if use_gamma else None
+    eps = 1e-5 if use_gamma else 0.0
+    y = ops.rmsnorm(x.cuda(), None if g is None else g.cuda(), eps)
+    rstd = torch.empty(rows, device="cuda")
+    ops.rmsnorm(x.cuda(), None, eps, rstd_out=rstd, stats_only=True)
+    ref = O.rmsnorm(x, g, eps)
+    assert_parity(y, ref, f"rmsnorm {rows}x{cols}")
+    ref_rstd = torch.rsqrt(x.float().pow(2).mean(-1) + eps)
+    assert (rstd.cpu() - ref_rstd).abs().max().item() <= 1e-5 * ref_rstd.abs().max().item()
+
+
+def test_rmsnorm_empty_strided_and_errors():
+    x = torch.randn(0, 64, device="cuda", dtype=BF)
+    assert ops.rmsnorm(x).shape == (0, 64)
+    big = torch.randn(6, 256, device="cuda", dtype=BF)
+    view = big[:, :128]                                   # row stride 256, 128 columns
+    out = torch.zeros(6, 128, device="cuda", dtype=BF)
+    ops.rmsnorm(view, None, 0.0, out=out)
+    assert_parity(out, O.rmsnorm(view.cpu()), "strided rows")
+    with pytest.raises(L.TrinityError, match="shape"):
+        ops.rmsnorm(torch.randn(4, 12, device="cuda", dtype=BF))           # cols not a multiple of 8
+    with pytest.raises(L.TrinityError, match="aligned"):
+        ops.rmsnorm(torch.randn(4, 72, device="cuda", dtype=BF)[:, 4:68])   # misaligned base
+
+
+PROJ_CASES = [
+    # B, M, P, N, Hq, Hkv, D, dtype, qk_norm, row_scale
+    (1, 128, 0, 64, 2, 2, 128, BF, False, False),
+    (1, 16, 4, 256, 2, 1, 128, HF, False, False),
+    (2, 200, 8, 512, 8, 2, 128, BF, False, True),
+    (1, 100, 0, 320, 5, 1, 64, BF, False, False),
+    (2, 96, 16, 512, 8, 2, 64, BF, True, False),
+    (2, 96, 16, 520, 4, 2, 128, HF, True, True),      # hidden size not a multiple of the 64-wide K step
+    (1, 16, 1024, 4544, 71, 71, 64, HF, False, False),
+]
+
+
+@pytest.mark.parametrize("B,M,P,N,Hq,Hkv,D,dt,qk_norm,rowscale", PROJ_CASES)
+def test_qkv_projection(B, M, P, N, Hq, Hkv, D, dt, qk_norm, rowscale):
+    torch.manual_seed(1)
+    x = torch.randn(B * M, N).to(dt)
+    wq, wk, wv = ((torch.randn(N, h * D) / N ** 0.5).to(dt) for h in (Hq, Hkv, Hkv))
+    rs = (torch.rand(B * M) + 0.5) if rowscale else None
+    gq = (1 + 0.1 * torch.randn(D)).to(dt) if qk_norm else None
+    gk = (1 + 0.1 * torch.randn(D)).to(dt) if qk_norm else None
+    q = torch.zeros(B, M, Hq, D, device="cuda", dtype=dt)
+    sentinel = 3.0
+    kc = torch.full((B, Hkv, P + M, D), sentinel, device="cuda", dtype=dt)
+    vc = torch.full((B, Hkv, P + M, D), sentinel, device="cuda", dtype=dt)
+    dev = lambda t: None if t is None else t.cuda()
+    ops.qkv_project(x.cuda(), wq.cuda(), wk.cuda(), wv.cuda(), q=ops.as_bshd(q, "bshd"),
+                    k_cache=ops.as_bshd(kc, "bhsd"), v_cache=ops.as_bshd(vc, "bhsd"), B=B, M=M, P=P, Hq=Hq, Hkv=Hkv,
+                    D=D, row_scale=dev(rs), qk_norm=qk_norm, qk_eps=1e-5, gamma_q=dev(gq), gamma_k=dev(gk))
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    xf = x.float() * (rs[:, None] if rs is not None else 1.0)
+    qr, kr, vr = O.project("qknorm" if qk_norm else "vanilla", xf, wq, wk, wv, B=B, M=M, Hq=Hq, Hkv=Hkv, D=D,
+                           qk_eps=1e-5, gamma_q=gq, gamma_k=gk)
+    assert_parity(q, qr.transpose(1, 2), "q")
+    assert_parity(kc[:, :, P:], kr, "k rows [P,P+M)")
+    assert_parity(vc[:, :, P:], vr, "v rows [P,P+M)")
+    # the cached prefix is left exactly as it was
+    assert bool((kc[:, :, :P] == sentinel).all()) and bool((vc[:, :, :P] == sentinel).all())
+
+
+ATTN_CASES = [
+    # B, M, P, Hq, Hkv, D, dtype, causal, scale
+    (1, 128, 0, 1, 1, 128, BF, False, None),
+    (1, 128, 0, 1, 1, 64, BF, False, None),
+    (1, 1, 0, 1, 1, 64, HF, True, None),              # a single query, a single key
+    (1, 256, 0, 2, 2, 128, BF, True, None),
+    (2, 300, 0, 4, 2, 128, HF, True, None),           # ragged: M not a multiple of the 128-row tile
+    (1, 16, 1024, 4, 4, 128, HF, False, 0.125),       # the reference's chunked-prefill shape
+    (1, 16, 1024, 3, 3, 64, HF, False, 0.125),
+    (2, 200, 72, 6, 2, 64, BF, True, None),           # prefix + causal + GQA
+    (1, 1000, 0, 8, 1, 64, BF, True, None),           # MQA
+    (1, 640, 0, 2, 1, 128, BF, True, 1.0),            # unscaled scores: large row maxima, O rescaling
+]
+
+
+def _attn_inputs(B, M, P, Hq, Hkv, D, dt, seed=2):
+    torch.manual_seed(seed)
+    L_ = P + M
+    return torch.randn(B, M, Hq, D).to(dt), torch.randn(B, Hkv, L_, D).to(dt), torch.randn(B, Hkv, L_, D).to(dt)
+
+
+def _run_attention(q, kc, vc, P, causal, scale, single_p=False, want_lse=True):
+    B, M, Hq, D = q.shape
+    o = torch.zeros(B, M, Hq, D, device="cuda", dtype=q.dtype)
+    lse = torch.zeros(B, Hq, M, device="cuda") if want_lse else None
+    ops.attention(ops.as_bshd(q.cuda(), "bshd"), ops.as_bshd(kc.cuda(), "bhsd"), ops.as_bshd(vc.cuda(), "bhsd"),
+                  ops.as_bshd(o, "bshd"), P=P, causal=causal, scale=scale, lse=lse, single_p=single_p)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    return o, lse
+
+
+@pytest.mark.parametrize("B,M,P,Hq,Hkv,D,dt,causal,scale", ATTN_CASES)
+def test_attention_core(B, M, P, Hq, Hkv, D, dt, causal, scale):
+    scale = D ** -0.5 if scale is None else scale
+    q, kc, vc = _attn_inputs(B, M, P, Hq, Hkv, D, dt)
+    o, lse = _run_attention(q, kc, vc, P, causal, scale)
+    r = O.attend(q.float().transpose(1, 2), kc.float(), vc.float(), P=P, causal=causal, scale=scale)
+    assert not torch.isnan(o).any()
+    assert_parity(o, r["out"].transpose(1, 2), "attention output")
+    sc = torch.matmul(q.float().transpose(1, 2), kc.float().repeat_interleave(Hq // Hkv, 1).transpose(-1, -2)) * scale
+    if causal:
+        i = torch.arange(M).view(M, 1)
+        j = torch.arange(P + M).view(1, P + M)
+        sc = sc.masked_fill(j > i + P, -math.inf)
+    lref = torch.logsumexp(sc, -1) / math.log(2)
+    assert (lse.cpu() - lref).abs().max().item() <= 1e-4
+
+
+def test_attention_single_p_mode_is_looser_but_bounded():
+    q, kc, vc = _attn_inputs(1, 256, 0, 2, 2, 128, BF)
+    r = O.attend(q.float().transpose(1, 2), kc.float(), vc.float(), P=0, causal=True, scale=128 ** -0.5)
+    o1, _ = _run_attention(q, kc, vc, 0, True, 128 ** -0.5, single_p=True)
+    o2, _ = _run_attention(q, kc, vc, 0, True, 128 ** -0.5, single_p=False)
+    a1, _ = parity_errors(o1, r["out"].transpose(1, 2))
+    a2, r2 = parity_errors(o2, r["out"].transpose(1, 2))
+    assert a1 <= 2e-2 and a2 <= 2e-2 and r2 <= 1e-2
+
+
+def test_attention_is_bitwise_reproducible():
+    q, kc, vc = _attn_inputs(2, 300, 40, 4, 2, 128, BF, seed=5)
+    o1, l1 = _run_attention(q, kc, vc, 40, True, 0.1)
+    o2, l2 = _run_attention(q, kc, vc, 40, True, 0.1)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+
+
+def test_attention_layouts_head_major_and_token_major_agree():
+    # the reference's tensors are head-major [H, M, D] (Q, O) or token-major [M, N] (O2): same numbers
+    q, kc, vc = _attn_inputs(1, 48, 16, 4, 4, 64, HF, seed=6)
+    o_tok, _ = _run_attention(q, kc, vc, 16, False, 1.0)
+    qh = q[0].permute(1, 0, 2).contiguous().cuda()              # [H, M, D]
+    oh = torch.zeros(4, 48, 64, device="cuda", dtype=HF)
+    ops.attention(ops.as_bshd(qh, "hsd"), ops.as_bshd(kc[0].cuda(), "hsd"), ops.as_bshd(vc[0].cuda(), "hsd"),
+                  ops.as_bshd(oh, "hsd"), P=16, causal=False, scale=1.0)
+    torch.cuda.synchronize()
+    assert torch.equal(oh.permute(1, 0, 2), o_tok[0])
+
+
+def test_attention_argument_errors():
+    q, kc, vc = _attn_inputs(1, 16, 0, 2, 2, 64, BF)
+    o = torch.zeros(1, 16, 2, 64, device="cuda", dtype=BF)
+    args = (ops.as_bshd(q.cuda(), "bshd"), ops.as_bshd(kc.cuda(), "bhsd"), ops.as_bshd(vc.cuda(), "bhsd"), ops.as_bshd(o, "bshd"))
+    with pytest.raises(L.TrinityError, match="shape"):
+        ops.attention(*args, P=0, causal=False, scale=0.0)                    # scale must be positive
+    q3 = torch.randn(1, 16, 3, 64, device="cuda", dtype=BF)
+    with pytest.raises(L.TrinityError, match="shape"):                        # 3 query heads over 2 kv heads
+        ops.attention(q3, args[1], args[2], torch.zeros_like(q3), P=0, causal=False, scale=1.0)
+    q96 = torch.randn(1, 16, 2, 96, device="cuda", dtype=BF)
+    with pytest.raises(L.TrinityError, match="shape"):                        # head_dim 96 unsupported
+        ops.attention(q96, q96.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3), q96, torch.zeros_like(q96),
+                      P=0, causal=False, scale=1.0)
+    assert L.kernel_status() == 0
+
+
+STATS_CASES = [
+    # variant, B, M, P, Hq, Hkv, D, dtype, causal, noise_mode, topk
+    ("roco", 1, 128, 0, 1, 1, 64, BF, False, 0, 16),
+    ("roco", 1, 256, 0, 2, 1, 64, BF, True, 0, 64),
+    ("roco", 2, 300, 40, 4, 2, 128, HF, True, 0, 100),
+    ("roco", 1, 16, 1024, 4, 4, 128, HF, False, 0, 128),
+    ("keyformer", 1, 128, 0, 1, 1, 128, BF, False, L.TRN_NOISE_TENSOR, 16),
+    ("keyformer", 1, 256, 0, 2, 1, 128, BF, True, L.TRN_NOISE_TENSOR, 64),
+    ("keyformer", 1, 256, 0, 2, 1, 128, BF, True, L.TRN_NOISE_GUMBEL, 64),
+    ("keyformer", 1, 16, 1024, 4, 4, 128, HF, False, L.TRN_NOISE_TENSOR, 128),
+    ("keyformer", 2, 300, 40, 4, 2, 64, BF, True, L.TRN_NOISE_GUMBEL, 100),
+]
+
+
+@pytest.mark.parametrize("variant,B,M,P,Hq,Hkv,D,dt,causal,noise_mode,topk", STATS_CASES)
+def test_key_statistics_and_topk(variant, B, M, P, Hq, Hkv, D, dt, causal, noise_mode, topk):
+    from gpu_util import run_block
+    torch.manual_seed(3)
+    L_ = P + M
+    scale = D ** -0.5
+    tau = 1.5 if variant == "keyformer" else 1.0
+    t = dict(Q=torch.randn(B, M, Hq, D).to(dt), K_cache=torch.randn(B, Hkv, L_, D).to(dt),
+             V_cache=torch.randn(B, Hkv, L_, D).to(dt), noise=None)
+    noise = None
+    if variant == "keyformer":
+        if noise_mode == L.TRN_NOISE_TENSOR:
+            t["noise"] = noise = torch.randn(B, Hq, M, L_).to(dt)
+        else:
+            noise = O.gumbel_noise(7, B, Hq, M, L_)
+    got = run_block(variant, t, B=B, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, causal=causal, scale=scale, tau=tau,
+                    noise_mode=noise_mode, seed=7, project=False)
+    r = O.attend(t["Q"].float().transpose(1, 2), t["K_cache"].float(), t["V_cache"].float(), P=P, causal=causal,
+                 scale=scale, variant=variant, tau=tau, noise=noise)
+    assert_parity(got["out"], r["out"].transpose(1, 2), "out")
+    # statistics are fp32 sums of fp32 probabilities: far tighter than the 16-bit tolerance
+    assert_parity(got["sum_p"], r["sum_p"], "sum_p", abs_tol=1e-4, rel_tol=1e-4)
+    if variant == "roco":
+        assert_parity(got["sum_p2"], r["sum_p2"], "sum_p2", abs_tol=1e-4, rel_tol=1e-4)
+        assert (got["sum_p"].sum(-1).cpu() - M).abs().max().item() <= 1e-3 * M       # rows of p sum to 1
+    # top-k: exact indices (order included) on the scores the kernel produced ...
+    idx = ops.topk_keys(got["sum_p"], topk)
+    torch.cuda.synchronize()
+    assert torch.equal(idx.cpu(), O.topk_keys(got["sum_p"].cpu(), topk))
+    # ... and the same selection as the oracle's own scores, except where two scores at the rank
+    # boundary are closer than the fp32 noise of the sums
+    want = O.topk_keys(r["sum_p"], topk)
+    if not torch.equal(idx.cpu(), want):
+        srt = torch.sort(r["sum_p"], -1, descending=True).values
+        gaps = (srt[..., :-1] - srt[..., 1:])
+        rows = (idx.cpu() != want).any(-1)
+        pos = (idx.cpu() != want)[rows].float().argmax(-1)
+        assert (gaps[rows].gather(-1, pos.clamp(max=gaps.shape[-1] - 1).unsqueeze(-1)) <= 1e-5 * srt[rows][..., :1]).all()
+
+
+def test_topk_edge_cases():
+    s = torch.tensor([[0.5, 2.0, 2.0, -1.0, 0.5, 3.0], [1.0, 1.0, 1.0, 1.0, 1.0, 1.0]], device="cuda")
+    assert ops.topk_keys(s, 4).cpu().tolist() == [[5, 1, 2, 0], [0, 1, 2, 3]]
+    assert ops.topk_keys(s, 6).cpu().tolist()[0] == [5, 1, 2, 0, 4, 3]
+    torch.manual_seed(9)
+    big = torch.randn(3, 8192, device="cuda")
+    big[1, 100:200] = big[1, 50]                         # a run of equal scores
+    assert torch.equal(ops.topk_keys(big, 2048).cpu(), O.topk_keys(big.cpu(), 2048))
+    odd = torch.randn(5, 1040, device="cuda")
+    assert torch.equal(ops.topk_keys(odd, 1).cpu(), O.topk_keys(odd.cpu(), 1))
+    with pytest.raises(L.TrinityError, match="shape"):
+        ops.topk_keys(torch.randn(2, 9000, device="cuda"), 10)
+    with pytest.raises(L.TrinityError, match="shape"):
+        ops.topk_keys(odd, 2000)
