@@ -33,6 +33,8 @@ if ROOT not in sys.path:
 WORKLOADS = {
     # name: variant, B, S, N, Hq, Hkv, D, project, topk
     "prenorm_llama": dict(variant="prenorm", B=8, S=2048, N=4096, Hq=32, Hkv=8, D=128, project=True, topk=0),
+    # one batch item of the above: the size used for ncu captures (inputs still exceed the L2)
+    "prenorm_llama_b1": dict(variant="prenorm", B=1, S=2048, N=4096, Hq=32, Hkv=8, D=128, project=True, topk=0),
     "vanilla_llama": dict(variant="vanilla", B=1, S=512, N=4096, Hq=32, Hkv=8, D=128, project=True, topk=0),
     "qknorm_falcon": dict(variant="qknorm", B=4, S=2048, N=4544, Hq=71, Hkv=1, D=64, project=True, topk=0),
     "keyformer_llama": dict(variant="keyformer", B=4, S=4096, N=0, Hq=32, Hkv=8, D=128, project=False, topk=1024),

@@ -103,11 +103,19 @@ def test_prenorm_config_sampled_parity():
     b = B - 1
     heads = slice(0, 4)            # kv group 0
     ts = dict(t)
-    r = O.attn_block("prenorm", X=t["X"].view(B, S, N)[b], Wq=t["WQ"][:, :4 * D], Wk=t["WK"][:, :D], Wv=t["WV"][:, :D],
-                     B=1, M=S, P=0, Hq=4, Hkv=1, D=D, causal=True, scale=D ** -0.5, pre_eps=1e-5,
-                     pre_gamma=t["pre_gamma"], round_to=BF, round_x_norm=BF)
-    assert_parity(got["out"][b, :, heads], r["out_bmhd"][0], "prenorm cfg out (16-bit storage points)")
     pure = O.attn_block("prenorm", X=t["X"].view(B, S, N)[b], Wq=t["WQ"][:, :4 * D], Wk=t["WK"][:, :D], Wv=t["WV"][:, :D],
                         B=1, M=S, P=0, Hq=4, Hkv=1, D=D, causal=True, scale=D ** -0.5, pre_eps=1e-5,
-                        pre_gamma=t["pre_gamma"])
-    assert_parity(got["out"][b, :, heads], pure["out_bmhd"][0], "prenorm cfg out (fp32 oracle)", rel_floor=1e-1)
+                        pre_gamma=t["pre_gamma"], round_x_norm=BF)
+    # X_norm, projection of the stored X_norm, attention on the stored q / k / v, then end to end
+    # (the steps of tests/test_gpu_block.py)
+    xn = got["plan"]._x_norm.view(B, S, N)[b]
+    assert_parity(xn, O.rmsnorm(t["X"].view(B, S, N)[b], t["pre_gamma"], 1e-5), "prenorm cfg X_norm")
+    qr, kr, vr = O.project("vanilla", xn.float().cpu(), t["WQ"][:, :4 * D], t["WK"][:, :D], t["WV"][:, :D], B=1, M=S,
+                           Hq=4, Hkv=1, D=D)
+    assert_parity(got["q"][b, :, heads], qr[0].transpose(0, 1), "prenorm cfg q")
+    assert_parity(got["k_cache"][b, 0], kr[0, 0], "prenorm cfg k")
+    assert_parity(got["v_cache"][b, 0], vr[0, 0], "prenorm cfg v")
+    strict = O.attend(got["q"][b:b + 1, :, heads].float().cpu().transpose(1, 2), got["k_cache"][b:b + 1, 0:1].float().cpu(),
+                      got["v_cache"][b:b + 1, 0:1].float().cpu(), P=0, causal=True, scale=D ** -0.5)
+    assert_parity(got["out"][b, :, heads], strict["out"][0].transpose(0, 1), "prenorm cfg out (attention on stored q/k/v)")
+    assert_parity(got["out"][b, :, heads], pure["out_bmhd"][0], "prenorm cfg out (fp32 oracle)", rel_floor=1e-1, rel_tol=5e-2)

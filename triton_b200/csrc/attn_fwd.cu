@@ -303,12 +303,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       mb *= p.scale_log2;                         // scale > 0, so max commutes with it
-      const float m_new = fmaxf(m_run, mb);
-      const bool grow = (m_new - m_run) > kRescaleThreshold;   // first block: m_run = -inf -> true
+      // m_run is the exponent offset in use: (row max seen at the last rescale) - kPBias.  fp16 has few
+      // exponent bits, so its p values are biased up by 2^4 to keep the low-order part of p out of
+      // the subnormal range; bf16 needs no bias.
+      constexpr float kPBias = (Io<T>::kFmt == 0) ? 4.0f : 0.0f;
+      const float m_target = mb - kPBias;
+      const bool grow = (m_target - m_run) > kRescaleThreshold;   // first block: m_run = -inf -> true
       float alpha = 1.0f;
       if (grow) {
-        alpha = ex2_approx(m_run - m_new);        // 0 on the first block
-        m_run = m_new;
+        alpha = ex2_approx(m_run - m_target);     // 0 on the first block
+        m_run = m_target;
       }
       // ---- P v of the previous block must be done: it reads the P buffer and accumulates into O
       if (j > 0) {

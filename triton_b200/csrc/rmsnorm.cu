@@ -158,9 +158,9 @@ int launch_typed(const TrnRmsArgs& a, cudaStream_t st, const DeviceState& ds) {
 }  // namespace
 
 int launch_rmsnorm(const TrnRmsArgs& a, cudaStream_t st, const DeviceState& ds) {
-  if (a.x == nullptr || (a.y == nullptr && a.rstd_out == nullptr)) return TRN_E_NULL;
   if (a.rows < 0 || a.cols <= 0 || (a.cols & 7) != 0 || a.cols > (1 << 24)) return TRN_E_SHAPE;
-  if (a.rows == 0) return TRN_OK;
+  if (a.rows == 0) return TRN_OK;      // nothing to do (an empty tensor may carry a null pointer)
+  if (a.x == nullptr || (a.y == nullptr && a.rstd_out == nullptr)) return TRN_E_NULL;
   if (a.x_row_stride < a.cols || (a.y != nullptr && a.y_row_stride < a.cols)) return TRN_E_SHAPE;
   if ((a.x_row_stride & 7) != 0 || (a.y != nullptr && (a.y_row_stride & 7) != 0)) return TRN_E_ALIGN;
   if (!aligned16(a.x) || !aligned16(a.y) || !aligned16(a.gamma)) return TRN_E_ALIGN;
