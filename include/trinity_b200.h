@@ -254,6 +254,33 @@ typedef struct {
 } TrnBlockHostArgs;
 int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * trinity_attn_block for callers that cannot provide (or allocate) a workspace.  It has no counterpart in
+ * the reference, whose harness allocates every tensor itself with torch.
+ *
+ * Who needs it: code that is handed only the operator's input and output buffers by its host runtime (a
+ * plugin inside an inference engine, a binding from a language with no device allocator at hand), or a
+ * serving loop that bans device allocation once it is warm because cudaMalloc synchronises the whole
+ * device.  For them the scratch of the block (row scales, log-sum-exp arrays) comes out of a fixed array
+ * inside the library: trinity_static_scratch_capacity() bytes (8 MiB), held by every GPU that loads the
+ * library until the process exits.
+ *
+ * Same arguments and results as trinity_attn_block; `workspace` / `workspace_bytes` are ignored.  x_norm
+ * (PreNorm with gamma) is still the caller's.  The call performs no cudaMalloc / cudaFree and calls no
+ * allocating routine.  Limits and rules:
+ *   - a problem whose trinity_attn_block_workspace() exceeds the capacity is refused with
+ *     TRN_E_STATIC_SCRATCH and nothing is launched (capacity covers B*M*(1+2*Hq) fp32 values up to ~2 M,
+ *     e.g. the PreNorm Llama configuration B=8, M=2048, Hq=32; not RoCo Falcon at B=2, M=8192, Hq=71);
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current): make that first call before any stream capture;
+ *   - all calls on a device share the one array, which keeps what the previous call left there.  Nothing in
+ *     it needs to be zero at entry (every value is written before it is read), but two calls that overlap
+ *     on the GPU — different streams, or a graph replay racing a direct call — race on it: serialise them.
+ * ---------------------------------------------------------------------------------------------- */
+#define TRN_E_STATIC_SCRATCH (-10) /* problem needs more scratch than the built-in array holds */
+size_t trinity_static_scratch_capacity(void);
+int trinity_attn_block_static(const TrnBlockArgs* a, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -24,6 +24,7 @@ EXPORTS = (
     "trinity_abi_version", "trinity_strerror", "trinity_last_cuda_error", "trinity_last_kernel_status",
     "trinity_rmsnorm", "trinity_qkv_project", "trinity_attention", "trinity_attn_colstats", "trinity_topk",
     "trinity_attn_block_workspace", "trinity_attn_block", "trinity_attn_block_host",
+    "trinity_static_scratch_capacity", "trinity_attn_block_static",
 )
 
 
@@ -135,12 +136,14 @@ def load() -> C.CDLL:
     for name, typ in (("trinity_rmsnorm", TrnRmsArgs), ("trinity_qkv_project", TrnProjArgs),
                       ("trinity_attention", TrnAttnArgs), ("trinity_attn_colstats", TrnColStatsArgs),
                       ("trinity_topk", TrnTopkArgs), ("trinity_attn_block", TrnBlockArgs),
-                      ("trinity_attn_block_host", TrnBlockHostArgs)):
+                      ("trinity_attn_block_host", TrnBlockHostArgs), ("trinity_attn_block_static", TrnBlockArgs)):
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(typ), C.c_void_p]
     lib.trinity_attn_block_workspace.restype = C.c_size_t
     lib.trinity_attn_block_workspace.argtypes = [C.POINTER(TrnBlockArgs)]
+    lib.trinity_static_scratch_capacity.restype = C.c_size_t
+    lib.trinity_static_scratch_capacity.argtypes = []
     if lib.trinity_abi_version() != ABI_VERSION:
         raise RuntimeError(f"{LIB_NAME} has ABI {lib.trinity_abi_version()}, binding expects {ABI_VERSION}")
     _lib = lib

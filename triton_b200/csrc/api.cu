@@ -164,6 +164,8 @@ const char* trinity_strerror(int code) {
     case TRN_E_CUDA: return "a CUDA call failed (see trinity_last_cuda_error)";
     case TRN_E_DEVICE: return "current device is not an sm_100 GPU";
     case TRN_E_KERNEL: return "a kernel reported a device-side status (a bounded wait ran out)";
+    case TRN_E_STATIC_SCRATCH:
+      return "problem needs more scratch than the library's built-in array holds (use trinity_attn_block with a workspace)";
     default: return "unknown error code";
   }
 }
