@@ -3,16 +3,21 @@
 // mapping query head h to kv head h / (Hq/Hkv).  Online softmax in fp32 (the reference's IR has no
 // max-subtraction, TritonGen.py:3071; the result is the same softmax, computed stably).
 //
-// One CTA = 128 queries of one head, streaming 128-key blocks:
-//   warp 0     TMA producer: q tile once, then k / v tiles into a ring (4-D descriptors, zero fill
-//              past the last key)
-//   warp 1     one lane issues tcgen05.mma: S = q k^T (fp32 in TMEM, two S buffers so the next
-//              block's q k^T overlaps this block's softmax) and O += P v (fp32 in TMEM)
-//   warps 2-5  one thread per query row: tcgen05.ld S, running max / sum, 2^x, P packed to 16-bit
-//              into swizzled shared memory as the A operand of P v; O is rescaled in TMEM only when
-//              a row's max grew by more than 2^8 since the last rescale.  By default p is split into
-//              two 16-bit parts (hi + lo) and P v is issued for both, so the product carries ~16
-//              mantissa bits of p instead of 8 (bf16) / 11 (fp16).
+// One CTA works on TWO 128-query tiles that read the same k / v stream, so that each SM sub-partition
+// hosts two softmax warps and the tensor pipe always has the other tile's MMAs to run:
+//   * GQA / MQA (Hq/Hkv >= 2): the tiles are the same 128 queries of two query heads of one kv group
+//     (identical causal structure: perfectly balanced);
+//   * MHA: the tiles are two consecutive 128-query blocks of one head.
+//   warp 0      TMA producer: both q tiles once, then k / v tiles into a ring (4-D descriptors, zero
+//               fill past the last key)
+//   warp 1      one lane issues tcgen05.mma: S_t = q_t k^T (fp32 in TMEM) and O_t += P_t v, where P_t is
+//               read from TENSOR MEMORY as the A operand (it overwrites S_t in place, no shared-memory
+//               round trip)
+//   warps 2-5   softmax warpgroup of tile 0, warps 6-9 of tile 1: one thread per query row; tcgen05.ld S,
+//               running max / sum, 2^x, p packed to 16 bits and written back over S with tcgen05.st.
+//               By default p is split into two 16-bit parts (hi + lo) and P v is issued for both, so the
+//               product carries ~16 mantissa bits of p.  O is rescaled in TMEM only when a row's max
+//               grew by more than 2^8 since the last rescale.
 // MODE 1 (KeyFormer's second row pass, ref_rms.py:172-174) computes only the log-sum-exp of the
 // perturbed scores (s + g) / tau and skips P, v and O.
 //
@@ -26,8 +31,8 @@ namespace {
 
 constexpr int BQ = 128;
 constexpr int BKV = 128;
-constexpr int kAttnThreads = 192;
-constexpr int kTmemColsAttn = 512;    // S0 [0,128) S1 [128,256) O [256, 256+D)
+constexpr int kAttnThreads = 320;
+constexpr int kTmemColsAttn = 512;    // S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D)
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 struct AttnParams {
@@ -35,8 +40,10 @@ struct AttnParams {
   void* o;
   long long o_sb, o_ss, o_sh;
   float* lse;
-  int B, M, P, L, Hq, group;
-  int n_qblocks;
+  int B, M, P, L, Hq, Hkv, group;
+  int n_qblocks;       // 128-row query blocks
+  int pair_heads;      // 1: tiles = two heads of a kv group; 0: tiles = two consecutive query blocks
+  int units;           // CTAs per query-block row (pairs, or batch*heads)
   int causal;
   float scale;         // MODE 1
   float scale_log2;    // MODE 0: scale * log2(e)
@@ -45,27 +52,29 @@ struct AttnParams {
   int* status;
 };
 
-template <int D, bool SPLIT>
+template <int D>
 struct AttnSmem {
   static constexpr int kStages = (D == 128) ? 2 : 4;
   static constexpr int kChunks = D / 64;
   static constexpr int kChunkBytes = 128 * 128;            // 128 rows x 64 elements
-  static constexpr int kQBytes = kChunks * kChunkBytes;
-  static constexpr int kKBytes = kQBytes;
-  static constexpr int kVBytes = kQBytes;
-  static constexpr int kPBytes = (SPLIT ? 4 : 2) * kChunkBytes;   // 128 rows x 128 keys (x2: hi and lo parts)
-  static constexpr int kQOff = 0;
-  static constexpr int kKVOff = kQBytes;
-  static constexpr int kPOff = kKVOff + kStages * (kKBytes + kVBytes);
-  static constexpr int kBarOff = kPOff + kPBytes;
+  static constexpr int kTileBytes = kChunks * kChunkBytes;
+  static constexpr int kQOff = 0;                          // two q tiles
+  static constexpr int kKVOff = 2 * kTileBytes;
+  static constexpr int kBarOff = kKVOff + kStages * 2 * kTileBytes;
   static constexpr int kTotal = kBarOff + 256 + 1024;
+};
+
+struct TileInfo {
+  int h;          // query head
+  int q0;         // first query row
+  int n_blocks;   // key blocks this tile visits (0: tile not present)
 };
 
 template <typename T, int D, int MODE, bool SPLIT>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
-  using SM = AttnSmem<D, SPLIT>;
+  using SM = AttnSmem<D>;
   constexpr int KS = SM::kStages;
   __shared__ int s_skip;
   if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(p.status);
@@ -76,15 +85,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bar_base = smem_base + SM::kBarOff;
-  // barriers: q_full, k_full[KS], v_full[KS], kv_empty[KS], s_full[2], s_free[2], p_full, pv_done
+  // barriers: q_full, k_full[KS], v_full[KS], kv_empty[KS], s_full[2], p_ready[2], pv_done[2]
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (1 + KS + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + 2 * KS + s); };
-  auto s_full = [&](int b) { return bar_base + 8u * (1 + 3 * KS + b); };
-  auto s_free = [&](int b) { return bar_base + 8u * (3 + 3 * KS + b); };
-  const uint32_t p_full = bar_base + 8u * (5 + 3 * KS);
-  const uint32_t pv_done = bar_base + 8u * (6 + 3 * KS);
+  auto s_full = [&](int t) { return bar_base + 8u * (1 + 3 * KS + t); };
+  auto p_ready = [&](int t) { return bar_base + 8u * (3 + 3 * KS + t); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (5 + 3 * KS + t); };
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + SM::kBarOff + 8 * (7 + 3 * KS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
@@ -99,12 +107,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(v_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full(b), 1);
-      mbar_init(s_free(b), 128);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full(t), 1);
+      mbar_init(p_ready(t), 128);
+      mbar_init(pv_done(t), 1);
     }
-    mbar_init(p_full, 128);
-    mbar_init(pv_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -117,22 +124,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  // ---- which tile: heavy (late) query blocks first so the causal tail is short
-  const int nbh = p.B * p.Hq;
-  const int qb = p.n_qblocks - 1 - static_cast<int>(blockIdx.x) / nbh;
-  const int bh = static_cast<int>(blockIdx.x) % nbh;
-  const int b = bh / p.Hq;
-  const int h = bh - b * p.Hq;
-  const int kvh = h / p.group;
-  const int q0 = qb * BQ;
-  const int q_hi = min(q0 + BQ, p.M);
-  const int kv_end = p.causal ? min(p.L, p.P + q_hi) : p.L;
-  const int n_blocks = (kv_end + BKV - 1) / BKV;
+  // ---- which two tiles: heavy (late) query blocks first so the causal tail is short
+  const int row_blk = static_cast<int>(blockIdx.x) / p.units;
+  const int unit = static_cast<int>(blockIdx.x) % p.units;
+  int b, kvh;
+  TileInfo tile[2];
+  if (p.pair_heads) {
+    const int pairs_per_group = (p.group + 1) >> 1;
+    const int pi = unit % pairs_per_group;
+    const int bk = unit / pairs_per_group;
+    kvh = bk % p.Hkv;
+    b = bk / p.Hkv;
+    const int qb = p.n_qblocks - 1 - row_blk;
+    tile[0].h = kvh * p.group + 2 * pi;
+    tile[1].h = tile[0].h + 1;
+    tile[0].q0 = tile[1].q0 = qb * BQ;
+    tile[0].n_blocks = 1;
+    tile[1].n_blocks = (2 * pi + 1 < p.group) ? 1 : 0;
+  } else {
+    const int n_qb2 = (p.n_qblocks + 1) >> 1;
+    const int qb2 = n_qb2 - 1 - row_blk;
+    b = unit / p.Hq;
+    const int h = unit - b * p.Hq;
+    kvh = h / p.group;
+    tile[0].h = tile[1].h = h;
+    tile[0].q0 = qb2 * 2 * BQ;
+    tile[1].q0 = tile[0].q0 + BQ;
+    tile[0].n_blocks = 1;
+    tile[1].n_blocks = (tile[1].q0 < p.M) ? 1 : 0;
+  }
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (tile[t].n_blocks) {
+      const int q_hi = min(tile[t].q0 + BQ, p.M);
+      const int kv_end = p.causal ? min(p.L, p.P + q_hi) : p.L;
+      tile[t].n_blocks = (kv_end + BKV - 1) / BKV;
+    }
+  }
+  const int n_max = max(tile[0].n_blocks, tile[1].n_blocks);
 
-  const uint32_t q_s = smem_base + SM::kQOff;
-  auto k_s = [&](int s) { return smem_base + SM::kKVOff + s * (SM::kKBytes + SM::kVBytes); };
-  auto v_s = [&](int s) { return k_s(s) + SM::kKBytes; };
-  const uint32_t p_s = smem_base + SM::kPOff;
+  auto q_s = [&](int t) { return smem_base + SM::kQOff + t * SM::kTileBytes; };
+  auto k_s = [&](int s) { return smem_base + SM::kKVOff + s * 2 * SM::kTileBytes; };
+  auto v_s = [&](int s) { return k_s(s) + SM::kTileBytes; };
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -140,24 +173,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       if (MODE == 0) tma_prefetch_desc(&tm_v);
-      mbar_expect_tx(q_full, SM::kQBytes);
+      const int n_tiles = (tile[0].n_blocks ? 1 : 0) + (tile[1].n_blocks ? 1 : 0);
+      mbar_expect_tx(q_full, n_tiles * SM::kTileBytes);
 #pragma unroll
-      for (int c = 0; c < SM::kChunks; ++c)
-        tma_load_head_tile(q_s + c * SM::kChunkBytes, &tm_q, q_full, p.qi, c * 64, q0, h, b);
+      for (int t = 0; t < 2; ++t) {
+        if (tile[t].n_blocks) {
+#pragma unroll
+          for (int c = 0; c < SM::kChunks; ++c)
+            tma_load_head_tile(q_s(t) + c * SM::kChunkBytes, &tm_q, q_full, p.qi, c * 64, tile[t].q0, tile[t].h, b);
+        }
+      }
     }
-    for (int j = 0; j < n_blocks; ++j) {
+    for (int j = 0; j < n_max; ++j) {
       const int st = j % KS;
       const uint32_t ph = (j / KS) & 1;
       bool ok = mbar_wait(kv_empty(st), ph ^ 1u, ctl, KST_TIMEOUT_PRODUCER);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (lane == 0) {
-        mbar_expect_tx(k_full(st), SM::kKBytes);
+        mbar_expect_tx(k_full(st), SM::kTileBytes);
 #pragma unroll
         for (int c = 0; c < SM::kChunks; ++c)
           tma_load_head_tile(k_s(st) + c * SM::kChunkBytes, &tm_k, k_full(st), p.ki, c * 64, j * BKV, kvh, b);
         if (MODE == 0) {
-          mbar_expect_tx(v_full(st), SM::kVBytes);
+          mbar_expect_tx(v_full(st), SM::kTileBytes);
 #pragma unroll
           for (int c = 0; c < SM::kChunks; ++c)
             tma_load_head_tile(v_s(st) + c * SM::kChunkBytes, &tm_v, v_full(st), p.vi, c * 64, j * BKV, kvh, b);
@@ -168,92 +207,103 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     constexpr uint32_t idesc_qk = make_idesc_f16(Io<T>::kFmt, 0, 0, BQ, BKV);   // q, k both K-major
-    constexpr uint32_t idesc_pv = make_idesc_f16(Io<T>::kFmt, 0, 1, BQ, D);     // P K-major, v MN-major
+    constexpr uint32_t idesc_pv = make_idesc_f16(Io<T>::kFmt, 0, 1, BQ, D);     // P (TMEM) K-major, v MN-major
     bool ok = mbar_wait(q_full, 0, ctl, KST_TIMEOUT_MMA);
     ok = __all_sync(0xffffffffu, ok);
-    // S[j & 1] = q k_j^T
-    auto issue_qk = [&](int j) -> bool {
-      const int st = j % KS;
-      const uint32_t ph = (j / KS) & 1;
-      bool w = mbar_wait(k_full(st), ph, ctl, KST_TIMEOUT_MMA);
-      w = w && mbar_wait(s_free(j & 1), ((j >> 1) & 1) ^ 1u, ctl, KST_TIMEOUT_MMA);
-      w = __all_sync(0xffffffffu, w);
-      if (!w) return false;
-      tc_fence_after();
+    // S_t = q_t k_j^T   (k_full(j) must have been waited for)
+    auto issue_qk = [&](int t, int j) {
       if (lane == 0) {
-        const uint32_t d_tmem = tmem_base + (j & 1) * BKV;
+        const int st = j % KS;
+        const uint32_t d_tmem = tmem_base + t * BKV;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * SM::kChunkBytes + (kk & 3) * 32;
-          umma_ss(d_tmem, make_smem_desc(q_s + off, 0, 1024), make_smem_desc(k_s(st) + off, 0, 1024), idesc_qk,
+          umma_ss(d_tmem, make_smem_desc(q_s(t) + off, 0, 1024), make_smem_desc(k_s(st) + off, 0, 1024), idesc_qk,
                   kk != 0 ? 1u : 0u);
         }
-        umma_commit(s_full(j & 1));
-        if (MODE == 1) umma_commit(kv_empty(st));
+        umma_commit(s_full(t));
       }
       __syncwarp();
-      return true;
     };
-    if (ok) ok = issue_qk(0);
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      if (j + 1 < n_blocks) {
-        ok = issue_qk(j + 1);
-        if (!ok) break;
-      }
-      if (MODE == 0) {
-        const int st = j % KS;
-        const uint32_t ph = (j / KS) & 1;
-        bool w = mbar_wait(v_full(st), ph, ctl, KST_TIMEOUT_MMA);
-        w = w && mbar_wait(p_full, j & 1, ctl, KST_TIMEOUT_MMA);
+    if (ok) {
+      ok = mbar_wait(k_full(0), 0, ctl, KST_TIMEOUT_MMA);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      for (int t = 0; t < 2; ++t)
+        if (tile[t].n_blocks) issue_qk(t, 0);
+    }
+    for (int j = 0; j < n_max && ok; ++j) {
+      const int st = j % KS;
+      const uint32_t ph = (j / KS) & 1;
+      bool k_next_ready = false;
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (j >= tile[t].n_blocks) continue;
+        // the softmax warpgroup of tile t is done with block j: P_t is in TMEM (MODE 0), S_t is consumed
+        bool w = mbar_wait(p_ready(t), j & 1, ctl, KST_TIMEOUT_MMA);
+        if (MODE == 0) w = w && mbar_wait(v_full(st), ph, ctl, KST_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
         tc_fence_after();
-        if (lane == 0) {
-          const uint32_t o_tmem = tmem_base + 2 * BKV;
-#pragma unroll
-          for (int kk = 0; kk < BKV / 16; ++kk) {
-            const uint64_t adesc = make_smem_desc(p_s + (kk >> 2) * SM::kChunkBytes + (kk & 3) * 32, 0, 1024);
-            const uint64_t bdesc = make_smem_desc(v_s(st) + kk * 2048, SM::kChunkBytes, 1024);
-            umma_ss(o_tmem, adesc, bdesc, idesc_pv, (j | kk) != 0 ? 1u : 0u);
-          }
-          if (SPLIT) {
-            // low-order part of P (p - hi), same v tile: O += P_lo v
+        if (MODE == 0) {
+          if (lane == 0) {
+            const uint32_t o_tmem = tmem_base + 2 * BKV + t * BKV;
+            const uint32_t p_tmem = tmem_base + t * BKV;
+            // P_t sits over S_t, per 32 score columns c: [hi of keys 32c..32c+31 | lo of the same keys],
+            // 16 columns (32 packed values) each.  One MMA consumes 16 keys = 8 columns.
 #pragma unroll
             for (int kk = 0; kk < BKV / 16; ++kk) {
-              const uint64_t adesc =
-                  make_smem_desc(p_s + (2 + (kk >> 2)) * SM::kChunkBytes + (kk & 3) * 32, 0, 1024);
+              const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
               const uint64_t bdesc = make_smem_desc(v_s(st) + kk * 2048, SM::kChunkBytes, 1024);
-              umma_ss(o_tmem, adesc, bdesc, idesc_pv, 1u);
+              umma_ts(o_tmem, p_tmem + a_col, bdesc, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+              if constexpr (SPLIT) umma_ts(o_tmem, p_tmem + a_col + 16, bdesc, idesc_pv, 1u);
             }
+            umma_commit(pv_done(t));
           }
-          umma_commit(kv_empty(st));
-          umma_commit(pv_done);
+          __syncwarp();
         }
-        __syncwarp();
+        if (j + 1 < tile[t].n_blocks) {
+          if (!k_next_ready) {
+            const int st1 = (j + 1) % KS;
+            const uint32_t ph1 = ((j + 1) / KS) & 1;
+            ok = mbar_wait(k_full(st1), ph1, ctl, KST_TIMEOUT_MMA);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            k_next_ready = true;
+          }
+          issue_qk(t, j + 1);
+        }
       }
+      if (!ok) break;
+      if (lane == 0) umma_commit(kv_empty(st));   // every MMA that read stage st has been issued
+      __syncwarp();
     }
   } else {
-    // ------------------------------- softmax / epilogue (warps 2..5) -------------------------------
-    const int quad = warp & 3;
+    // ------------------------------- softmax / epilogue (warps 2..9) -------------------------------
+    const int t = (warp - 2) >> 2;                 // which tile this warpgroup owns
+    const int quad = warp & 3;                     // TMEM lane quarter of this warp
     const int row = quad * 32 + lane;
-    const int q_abs = q0 + row;
+    const int q_abs = tile[t].q0 + row;
+    const int h = tile[t].h;
+    const int n_blocks = tile[t].n_blocks;
     const bool row_valid = q_abs < p.M;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const int limit = p.causal ? min(p.P + q_abs, p.L - 1) : p.L - 1;       // last visible key of this row
-    const int limit_min = p.causal ? min(p.P + q0, p.L - 1) : p.L - 1;      // ... of the tile's first row
-    uint8_t* p_gen = smem_gen + SM::kPOff;
+    const int limit = p.causal ? min(p.P + q_abs, p.L - 1) : p.L - 1;               // last visible key of this row
+    const int limit_min = p.causal ? min(p.P + tile[t].q0, p.L - 1) : p.L - 1;     // ... of the tile's first row
+    const uint32_t s_tmem = tmem_base + t * BKV + lane_addr;
+    const uint32_t o_tmem = tmem_base + 2 * BKV + t * BKV + lane_addr;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     uint32_t r[32];
 
     for (int j = 0; j < n_blocks; ++j) {
-      const int sb = j & 1;
       const int kv0 = j * BKV;
-      ok = mbar_wait(s_full(sb), (j >> 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
+      ok = mbar_wait(s_full(t), j & 1, ctl, KST_TIMEOUT_CONSUMER);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_tmem = tmem_base + sb * BKV + lane_addr;
       const bool masked = (kv0 + BKV - 1) > limit_min;
 
       if (MODE == 1) {
@@ -261,7 +311,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int c = 0; c < BKV / 32; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
-          float t[32];
+          float tv[32];
           float cm = -INFINITY;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -271,35 +321,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               const float g = row_valid ? noise_at<T>(p.noise, b, h, q_abs, col) : 0.f;
               v = (__uint_as_float(r[i]) * p.scale + g) * p.pert_log2;
             }
-            t[i] = v;
+            tv[i] = v;
             cm = fmaxf(cm, v);
           }
           const float m_new = fmaxf(m_run, cm);
           if (m_new != -INFINITY) {
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc += ex2_approx(t[i] - m_new);
+            for (int i = 0; i < 32; ++i) acc += ex2_approx(tv[i] - m_new);
             l_run = l_run * ex2_approx(m_run - m_new) + acc;
             m_run = m_new;
           }
         }
         tc_fence_before();
-        mbar_arrive(s_free(sb));
+        mbar_arrive(p_ready(t));
         continue;
       }
 
       // ---- pass 1: block maximum of this row
       float mb = -INFINITY;
-      for (int c = 0; c < BKV / 32; ++c) {
-        tmem_ld32(s_tmem + c * 32, r);
-        tmem_wait_ld();
-        if (masked) {
+      if (masked) {
+        for (int c = 0; c < BKV / 32; ++c) {
+          tmem_ld32(s_tmem + c * 32, r);
+          tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (kv0 + c * 32 + i <= limit) mb = fmaxf(mb, __uint_as_float(r[i]));
-        } else {
+        }
+      } else {
+        for (int c = 0; c < BKV / 32; ++c) {
+          tmem_ld32(s_tmem + c * 32, r);
+          tmem_wait_ld();
+          float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mb = fmaxf(mb, __uint_as_float(r[i]));
+          for (int i = 2; i < 32; i += 2) {
+            m0 = fmaxf(m0, __uint_as_float(r[i]));
+            m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+          }
+          mb = fmaxf(mb, fmaxf(m0, m1));
         }
       }
       mb *= p.scale_log2;                         // scale > 0, so max commutes with it
@@ -314,76 +373,62 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         alpha = ex2_approx(m_run - m_target);     // 0 on the first block
         m_run = m_target;
       }
-      // ---- P v of the previous block must be done: it reads the P buffer and accumulates into O
-      if (j > 0) {
-        ok = mbar_wait(pv_done, (j - 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, grow)) {
-          const uint32_t o_tmem = tmem_base + 2 * BKV + lane_addr;
+      // S_t(j) was produced after P_t(j-1) v (MMAs run in issue order), so O_t is quiescent here
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            tmem_ld32(o_tmem + c * 32, r);
-            tmem_wait_ld();
+        for (int c = 0; c < D / 32; ++c) {
+          tmem_ld32(o_tmem + c * 32, r);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(o_tmem + c * 32, r);
-          }
-          tmem_wait_st();
-          l_run *= alpha;
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(o_tmem + c * 32, r);
         }
+        l_run *= alpha;
       }
-      // ---- pass 2: p = 2^(s * c - m), row sum, P tile into swizzled shared memory
-      float lsum = 0.f;
+      // ---- pass 2: p = 2^(s * c - m), row sum, P written over S (hi | lo per 32 score columns)
+      float lsum0 = 0.f, lsum1 = 0.f;
+      const float neg_m = -m_run;
+#pragma unroll 1
       for (int c = 0; c < BKV / 32; ++c) {
         tmem_ld32(s_tmem + c * 32, r);
         tmem_wait_ld();
-        uint32_t packed[16];
-        uint32_t packed_lo[SPLIT ? 16 : 1];
+        uint32_t pk[SPLIT ? 32 : 16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_run));
-          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_run));
+          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
           if (masked) {
             if (kv0 + c * 32 + i > limit) p0 = 0.f;
             if (kv0 + c * 32 + i + 1 > limit) p1 = 0.f;
           }
-          lsum += p0 + p1;
+          lsum0 += p0;
+          lsum1 += p1;
           const uint32_t hi = Io<T>::pack2(p0, p1);
-          packed[i >> 1] = hi;
-          if (SPLIT) {
+          pk[i >> 1] = hi;
+          if constexpr (SPLIT) {
             // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
             const float2 hf = Io<T>::unpack2(hi);
-            packed_lo[i >> 1] = Io<T>::pack2(p0 - hf.x, p1 - hf.y);
+            pk[16 + (i >> 1)] = Io<T>::pack2(p0 - hf.x, p1 - hf.y);
           }
         }
-        uint8_t* chunk = p_gen + (c >> 1) * SM::kChunkBytes;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint32_t unit = static_cast<uint32_t>((c & 1) * 4 + u);
-          const uint32_t off = swz128(static_cast<uint32_t>(row), unit);
-          *reinterpret_cast<uint4*>(chunk + off) =
-              make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
-          if (SPLIT)
-            *reinterpret_cast<uint4*>(chunk + 2 * SM::kChunkBytes + off) =
-                make_uint4(packed_lo[4 * u], packed_lo[4 * u + 1], packed_lo[4 * u + 2], packed_lo[4 * u + 3]);
+        if constexpr (SPLIT) {
+          tmem_st32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(pk));
+        } else {
+          tmem_st16(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[16]>(pk));
         }
       }
-      l_run += lsum;
+      l_run += lsum0 + lsum1;
+      tmem_wait_st();
       tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(s_free(sb));
-      mbar_arrive(p_full);
+      mbar_arrive(p_ready(t));
     }
 
-    if (ok && MODE == 0) {
-      ok = mbar_wait(pv_done, (n_blocks - 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
+    if (ok && MODE == 0 && n_blocks > 0) {
+      ok = mbar_wait(pv_done(t), (n_blocks - 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
         const float inv_l = 1.0f / l_run;
-        const uint32_t o_tmem = tmem_base + 2 * BKV + lane_addr;
         T* orow = static_cast<T*>(p.o) + static_cast<long long>(b) * p.o_sb + static_cast<long long>(q_abs) * p.o_ss +
                   static_cast<long long>(h) * p.o_sh;
 #pragma unroll 1
@@ -405,7 +450,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_before();
       }
     }
-    if (ok && row_valid && p.lse != nullptr)
+    if (ok && n_blocks > 0 && row_valid && p.lse != nullptr)
       p.lse[(static_cast<long long>(b) * p.Hq + h) * p.M + q_abs] = m_run + log2f(l_run);
   }
 
@@ -424,7 +469,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 template <typename T, int D, int MODE, bool SPLIT>
 int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
-  using SM = AttnSmem<D, SPLIT>;
+  using SM = AttnSmem<D>;
   AttnParams p{};
   const int L = a.P + a.M;
   CUtensorMap tm_q, tm_k, tm_v;
@@ -442,8 +487,17 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   p.o = a.o.ptr;
   p.o_sb = a.o.stride_b; p.o_ss = a.o.stride_s; p.o_sh = a.o.stride_h;
   p.lse = a.lse;
-  p.B = a.B; p.M = a.M; p.P = a.P; p.L = L; p.Hq = a.Hq; p.group = a.Hq / a.Hkv;
+  p.B = a.B; p.M = a.M; p.P = a.P; p.L = L; p.Hq = a.Hq; p.Hkv = a.Hkv; p.group = a.Hq / a.Hkv;
   p.n_qblocks = (a.M + BQ - 1) / BQ;
+  p.pair_heads = p.group >= 2 ? 1 : 0;
+  long long rows_of_ctas;
+  if (p.pair_heads) {
+    p.units = a.B * a.Hkv * ((p.group + 1) / 2);
+    rows_of_ctas = p.n_qblocks;
+  } else {
+    p.units = a.B * a.Hq;
+    rows_of_ctas = (p.n_qblocks + 1) / 2;
+  }
   p.causal = a.causal;
   p.scale = a.scale;
   p.scale_log2 = a.scale * 1.4426950408889634f;
@@ -457,7 +511,7 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   auto kern = attn_fwd_kernel<T, D, MODE, SPLIT>;
   rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
   if (rc != TRN_OK) return rc;
-  const long long grid = static_cast<long long>(p.n_qblocks) * a.B * a.Hq;
+  const long long grid = rows_of_ctas * p.units;
   if (grid > 0x7fffffffLL) return TRN_E_SHAPE;
   kern<<<static_cast<int>(grid), kAttnThreads, SM::kTotal, st>>>(tm_q, tm_k, tm_v, p);
   TRN_CUDA_TRY(cudaGetLastError());
