@@ -60,6 +60,13 @@ __device__ __forceinline__ void tma_load_head_tile(uint32_t dst, const CUtensorM
   tma_load_4d(dst, m, bar, c[0], c[1], c[2], c[3]);
 }
 
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

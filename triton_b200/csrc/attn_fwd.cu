@@ -24,6 +24,8 @@
 // Algorithmic flops per launch (MODE 0): 4 * B * Hq * D * (number of visible (query, key) pairs).
 #include <math.h>
 
+#include <type_traits>
+
 #include "attn_common.cuh"
 
 namespace trn {
@@ -352,13 +354,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int c = 0; c < BKV / 32; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
-          float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]);
+          float m0 = fmaxf(__uint_as_float(r[0]), __uint_as_float(r[1]));
+          float m1 = fmaxf(__uint_as_float(r[2]), __uint_as_float(r[3]));
 #pragma unroll
-          for (int i = 2; i < 32; i += 2) {
-            m0 = fmaxf(m0, __uint_as_float(r[i]));
-            m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+          for (int i = 4; i < 32; i += 4) {
+            m0 = fmax3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+            m1 = fmax3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
           }
-          mb = fmaxf(mb, fmaxf(m0, m1));
+          mb = fmax3(mb, m0, m1);
         }
       }
       mb *= p.scale_log2;                         // scale > 0, so max commutes with it
@@ -385,39 +388,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         l_run *= alpha;
       }
-      // ---- pass 2: p = 2^(s * c - m), row sum, P written over S (hi | lo per 32 score columns)
-      float lsum0 = 0.f, lsum1 = 0.f;
-      const float neg_m = -m_run;
+      // ---- pass 2: p = 2^(s * c - m), row sum, P written over S (hi | lo per 32 score columns).
+      //      Arithmetic on pairs of columns uses the packed fp32x2 instructions of sm_100.
+      float2 lsum = make_float2(0.f, 0.f);
+      const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 neg_m2 = make_float2(-m_run, -m_run);
+      const float2 minus1 = make_float2(-1.f, -1.f);
+      // compiled twice: the unmasked version carries no per-element compare / select
+      auto pass2 = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        tmem_ld32(s_tmem + c * 32, r);
-        tmem_wait_ld();
-        uint32_t pk[SPLIT ? 32 : 16];
+        for (int c = 0; c < BKV / 32; ++c) {
+          tmem_ld32(s_tmem + c * 32, r);
+          tmem_wait_ld();
+          uint32_t pk[SPLIT ? 32 : 16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
-          if (masked) {
-            if (kv0 + c * 32 + i > limit) p0 = 0.f;
-            if (kv0 + c * 32 + i + 1 > limit) p1 = 0.f;
+          for (int i = 0; i < 32; i += 2) {
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, neg_m2);
+            float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            if constexpr (kMasked) {
+              if (kv0 + c * 32 + i > limit) pp.x = 0.f;
+              if (kv0 + c * 32 + i + 1 > limit) pp.y = 0.f;
+            }
+            lsum = __fadd2_rn(lsum, pp);
+            const uint32_t hi = Io<T>::pack2(pp.x, pp.y);
+            pk[i >> 1] = hi;
+            if constexpr (SPLIT) {
+              // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
+              const float2 lo = __ffma2_rn(Io<T>::unpack2(hi), minus1, pp);    // p - hi, exact
+              pk[16 + (i >> 1)] = Io<T>::pack2(lo.x, lo.y);
+            }
           }
-          lsum0 += p0;
-          lsum1 += p1;
-          const uint32_t hi = Io<T>::pack2(p0, p1);
-          pk[i >> 1] = hi;
           if constexpr (SPLIT) {
-            // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
-            const float2 hf = Io<T>::unpack2(hi);
-            pk[16 + (i >> 1)] = Io<T>::pack2(p0 - hf.x, p1 - hf.y);
+            tmem_st32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(pk));
+          } else {
+            tmem_st16(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[16]>(pk));
           }
         }
-        if constexpr (SPLIT) {
-          tmem_st32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(pk));
-        } else {
-          tmem_st16(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[16]>(pk));
-        }
-      }
-      l_run += lsum0 + lsum1;
+      };
+      if (masked) pass2(std::true_type{});
+      else pass2(std::false_type{});
+      l_run += lsum.x + lsum.y;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_ready(t));
