@@ -8,8 +8,11 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
+import os
+
 LIB_NAME = "libtrinity_b200.so"
-LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
+# TRINITY_B200_LIB points at another build of the same library (e.g. one compiled with extra -D flags)
+LIB_PATH = Path(os.environ.get("TRINITY_B200_LIB") or (Path(__file__).resolve().parent / LIB_NAME))
 
 ABI_VERSION = 1
 

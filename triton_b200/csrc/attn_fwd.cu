@@ -37,6 +37,7 @@ constexpr int kAttnThreads = 320;
 constexpr int kTmemColsAttn = 512;    // S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D)
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
+
 struct AttnParams {
   HeadMapInfo qi, ki, vi;
   void* o;
@@ -87,15 +88,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bar_base = smem_base + SM::kBarOff;
-  // barriers: q_full, k_full[KS], v_full[KS], kv_empty[KS], s_full[2], p_ready[2], pv_done[2]
+  // barriers: q_full, k_full[KS], v_full[KS], kv_empty[KS], s_full[2], pv_done[2], p_ready[2 tiles][2 halves]
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (1 + KS + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + 2 * KS + s); };
   auto s_full = [&](int t) { return bar_base + 8u * (1 + 3 * KS + t); };
-  auto p_ready = [&](int t) { return bar_base + 8u * (3 + 3 * KS + t); };
-  auto pv_done = [&](int t) { return bar_base + 8u * (5 + 3 * KS + t); };
-  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + SM::kBarOff + 8 * (7 + 3 * KS));
+  auto pv_done = [&](int t) { return bar_base + 8u * (3 + 3 * KS + t); };
+  // P of a block becomes ready in two halves (keys 0..63, 64..127) so that P v starts on the first half
+  // while the softmax threads still work on the second
+  auto p_ready = [&](int t, int half) { return bar_base + 8u * (5 + 3 * KS + 2 * t + half); };
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + SM::kBarOff + 8 * (9 + 3 * KS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -111,7 +114,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_ready(t), 128);
+      mbar_init(p_ready(t, 0), 128);
+      mbar_init(p_ready(t, 1), 128);
       mbar_init(pv_done(t), 1);
     }
     *abort_flag = 0;
@@ -242,28 +246,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool k_next_ready = false;
       for (int t = 0; t < 2 && ok; ++t) {
         if (j >= tile[t].n_blocks) continue;
-        // the softmax warpgroup of tile t is done with block j: P_t is in TMEM (MODE 0), S_t is consumed
-        bool w = mbar_wait(p_ready(t), j & 1, ctl, KST_TIMEOUT_MMA);
-        if (MODE == 0) w = w && mbar_wait(v_full(st), ph, ctl, KST_TIMEOUT_MMA);
-        ok = __all_sync(0xffffffffu, w);
-        if (!ok) break;
-        tc_fence_after();
         if (MODE == 0) {
-          if (lane == 0) {
-            const uint32_t o_tmem = tmem_base + 2 * BKV + t * BKV;
-            const uint32_t p_tmem = tmem_base + t * BKV;
-            // P_t sits over S_t, per 32 score columns c: [hi of keys 32c..32c+31 | lo of the same keys],
-            // 16 columns (32 packed values) each.  One MMA consumes 16 keys = 8 columns.
+          bool w = mbar_wait(v_full(st), ph, ctl, KST_TIMEOUT_MMA);
+          ok = __all_sync(0xffffffffu, w);
+          if (!ok) break;
+          const uint32_t o_tmem = tmem_base + 2 * BKV + t * BKV;
+          const uint32_t p_tmem = tmem_base + t * BKV;
 #pragma unroll
-            for (int kk = 0; kk < BKV / 16; ++kk) {
-              const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
-              const uint64_t bdesc = make_smem_desc(v_s(st) + kk * 2048, SM::kChunkBytes, 1024);
-              umma_ts(o_tmem, p_tmem + a_col, bdesc, idesc_pv, (j | kk) != 0 ? 1u : 0u);
-              if constexpr (SPLIT) umma_ts(o_tmem, p_tmem + a_col + 16, bdesc, idesc_pv, 1u);
+          for (int half = 0; half < 2; ++half) {
+            // first / second 64 keys of P_t(j) are in TMEM
+            ok = mbar_wait(p_ready(t, half), j & 1, ctl, KST_TIMEOUT_MMA);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+              // P_t sits over S_t, per 32 score columns c: [hi of keys 32c..32c+31 | lo of the same keys],
+              // 16 columns (32 packed values) each.  One MMA consumes 16 keys = 8 columns.
+#pragma unroll
+              for (int k4 = 0; k4 < BKV / 32; ++k4) {
+                const int kk = half * (BKV / 32) + k4;
+                const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
+                const uint64_t bdesc = make_smem_desc(v_s(st) + kk * 2048, SM::kChunkBytes, 1024);
+                umma_ts(o_tmem, p_tmem + a_col, bdesc, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+                if constexpr (SPLIT) umma_ts(o_tmem, p_tmem + a_col + 16, bdesc, idesc_pv, 1u);
+              }
+              if (half == 1) umma_commit(pv_done(t));
             }
-            umma_commit(pv_done(t));
+            __syncwarp();
           }
-          __syncwarp();
+          if (!ok) break;
+        } else {
+          // the softmax warpgroup of tile t has consumed S_t(j)
+          ok = mbar_wait(p_ready(t, 1), j & 1, ctl, KST_TIMEOUT_MMA);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
         }
         if (j + 1 < tile[t].n_blocks) {
           if (!k_next_ready) {
@@ -336,7 +353,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
         tc_fence_before();
-        mbar_arrive(p_ready(t));
+        mbar_arrive(p_ready(t, 1));
         continue;
       }
 
@@ -424,6 +441,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           } else {
             tmem_st16(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[16]>(pk));
           }
+          if (c == 1) {            // keys 0..63 of P are written: let P v begin
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(p_ready(t, 0));
+          }
         }
       };
       if (masked) pass2(std::true_type{});
@@ -431,7 +453,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       l_run += lsum.x + lsum.y;
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_ready(t));
+      mbar_arrive(p_ready(t, 1));
     }
 
     if (ok && MODE == 0 && n_blocks > 0) {
@@ -549,6 +571,7 @@ bool ht_ok(const TrnHeadTensor& t) {
 }
 
 }  // namespace
+
 
 int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (a.B <= 0 || a.M <= 0 || a.P < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.Hq % a.Hkv != 0) return TRN_E_SHAPE;
