@@ -39,6 +39,9 @@ WORKLOADS = {
     "qknorm_falcon": dict(variant="qknorm", B=4, S=2048, N=4544, Hq=71, Hkv=1, D=64, project=True, topk=0),
     "keyformer_llama": dict(variant="keyformer", B=4, S=4096, N=0, Hq=32, Hkv=8, D=128, project=False, topk=1024),
     "roco_falcon": dict(variant="roco", B=2, S=8192, N=0, Hq=71, Hkv=1, D=64, project=False, topk=2048),
+    # standalone RMSNorm (HBM-bound): rows x cols, bf16, eps 1e-5, gamma
+    "rmsnorm_llama": dict(variant="rmsnorm", rows=16384, cols=4096),
+    "rmsnorm_falcon": dict(variant="rmsnorm", rows=8192, cols=4544),
 }
 METRIC = "fused attn-block TFLOP/s"
 
@@ -366,6 +369,53 @@ def run_ours(args, w):
 TRAFFIC_BYTES = {}
 
 
+def run_rmsnorm(args, w):
+    """Standalone RMSNorm: algorithmic bytes = 2 * rows * cols * 2 (read x, write y) + gamma."""
+    import torch
+    from triton_b200 import _lib as L
+    from triton_b200 import ops
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if int(os.environ.get("RANK", "0")) != 0 or world != 1:
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+    torch.cuda.set_device(local)
+    rows, cols = w["rows"], w["cols"]
+    dt = torch.bfloat16
+    x = torch.randn(rows, cols, device="cuda").to(dt)
+    g = (1 + 0.1 * torch.randn(cols, device="cuda")).to(dt)
+    y = torch.empty_like(x)
+    stream = torch.cuda.current_stream()
+    for _ in range(max(args.warmup, 3)):
+        ops.rmsnorm(x, g, 1e-5, out=y)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        ops.rmsnorm(x, g, 1e-5, out=y)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    nbytes = 2 * rows * cols * 2 + cols * 2
+    peaks = measured_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    if L.kernel_status() != 0:
+        raise RuntimeError("kernel status")
+    line = {"metric": "rmsnorm GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "us_per_call": ms * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "rows": rows, "cols": cols, "eps": 1e-5, "gamma": True,
+                       "l2": "x and y (2 x %.0f MB) are larger than the 126 MB L2" % (rows * cols * 2 / 1e6)},
+            "clocks": clocks, "gpu_launches": args.steps, "e2e": None,
+            "roofline": {"kernel": "rmsnorm_cta_kernel", "bound": "hbm", "achieved": gbs, "peak": peaks["hbm"],
+                         "unit": "GB/s", "frac": gbs / peaks["hbm"], "peak_source": peaks["kind"],
+                         "traffic": TRAFFIC_BYTES.get(args.workload)}}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -376,7 +426,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "reference":
+    if w["variant"] == "rmsnorm":
+        run_rmsnorm(args, w)
+    elif args.impl == "reference":
         run_reference(args, w)
     else:
         run_ours(args, w)
