@@ -47,7 +47,7 @@ def rmsnorm(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, eps: float = 
 
 
 # ------------------------------------------------------------------------------------------------
-# Counter-based Gumbel noise: host restatement of noise_bits / gumbel_from_bits in
+# Counter-based Gumbel noise: host restatement of the noise functions in
 # triton_b200/csrc/attn_common.cuh (same integer mixing; logs in float64, result rounded to fp32)
 # ------------------------------------------------------------------------------------------------
 def _mix32(x: np.ndarray) -> np.ndarray:
@@ -60,16 +60,19 @@ def _mix32(x: np.ndarray) -> np.ndarray:
     return x
 
 
-def noise_bits(seed: int, idx: np.ndarray) -> np.ndarray:
-    idx = idx.astype(np.uint64)
-    lo = (idx & np.uint64(0xFFFFFFFF)).astype(np.uint32)
-    hi = (idx >> np.uint64(32)).astype(np.uint32)
+def noise_bits(seed: int, bh: np.ndarray, i: np.ndarray, j: np.ndarray) -> np.ndarray:
+    """32 hashed bits of element (b*Hq+h, query i, key j): headkey -> rowhash -> per-element mix, the integer
+    steps of noise_headkey / noise_rowhash / noise_elem_bits in triton_b200/csrc/attn_common.cuh."""
     s_lo = np.uint32(seed & 0xFFFFFFFF)
     s_hi = np.uint32((seed >> 32) & 0xFFFFFFFF)
     with np.errstate(over="ignore"):
-        h = _mix32(lo ^ s_lo)
-        h ^= hi + s_hi * np.uint32(0x9E3779B9)
-        return _mix32(h + np.uint32(0x85EBCA6B))
+        headkey = _mix32(s_lo ^ _mix32(bh.astype(np.uint32) + s_hi * np.uint32(0x9E3779B9)))
+        rowhash = _mix32(headkey + i.astype(np.uint32) * np.uint32(0x9E3779B9))
+        x = rowhash ^ (j.astype(np.uint32) * np.uint32(0x85EBCA6B))
+        x = x ^ (x >> np.uint32(16))
+        x = x * np.uint32(0x7FEB352D)
+        x = x ^ (x >> np.uint32(15))
+    return x
 
 
 def gumbel_noise(seed: int, B: int, Hq: int, M: int, L: int, b0: int = 0, b1: Optional[int] = None,
@@ -77,12 +80,11 @@ def gumbel_noise(seed: int, B: int, Hq: int, M: int, L: int, b0: int = 0, b1: Op
     """Gumbel(0,1) field [b1-b0, h1-h0, M, L] of the [B, Hq, M, L] noise the kernels generate from `seed`."""
     b1 = B if b1 is None else b1
     h1 = Hq if h1 is None else h1
-    bb = np.arange(b0, b1, dtype=np.uint64)[:, None, None, None]
-    hh = np.arange(h0, h1, dtype=np.uint64)[None, :, None, None]
-    ii = np.arange(M, dtype=np.uint64)[None, None, :, None]
-    jj = np.arange(L, dtype=np.uint64)[None, None, None, :]
-    idx = ((bb * np.uint64(Hq) + hh) * np.uint64(M) + ii) * np.uint64(L) + jj
-    bits = noise_bits(seed, idx)
+    bb = np.arange(b0, b1, dtype=np.uint32)[:, None, None, None]
+    hh = np.arange(h0, h1, dtype=np.uint32)[None, :, None, None]
+    ii = np.arange(M, dtype=np.uint32)[None, None, :, None]
+    jj = np.arange(L, dtype=np.uint32)[None, None, None, :]
+    bits = noise_bits(seed, bb * np.uint32(Hq) + hh, ii, jj)
     u = ((bits >> np.uint32(9)).astype(np.float64) + 0.5) * 2.0 ** -23
     g = -np.log(-np.log(u))
     return torch.from_numpy(g.astype(np.float32))

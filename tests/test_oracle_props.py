@@ -85,7 +85,8 @@ def test_gumbel_noise_is_deterministic_sliceable_and_gumbel():
     g = O.gumbel_noise(5, 1, 8, 128, 512).double()
     assert abs(g.mean().item() - 0.5772) < 0.01 and abs(g.var().item() - math.pi ** 2 / 6) < 0.03
     # known-answer: the integer mixing behind the field (matches the device function bit for bit)
-    bits = O.noise_bits(7, np.array([0, 1, 2 ** 33 + 5], dtype=np.uint64))
+    bits = O.noise_bits(7, np.array([0, 0, 3], dtype=np.uint32), np.array([0, 1, 5], dtype=np.uint32),
+                        np.array([0, 0, 9], dtype=np.uint32))
     assert bits.dtype == np.uint32 and len(set(bits.tolist())) == 3
 
 

@@ -74,10 +74,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 // ------------------------------------------------------------------------------------------
-// KeyFormer noise.  Counter-based: element (b, h, query i, key j) of a [B, Hq, M, L] noise field
-// gets 32 hashed bits from (seed, linear index); 23 of them make u in (0,1) and
-// g = -log(-log(u)) ~ Gumbel(0,1).  The host restatement of this function (same integer mixing,
-// float64 logs) lives with the parity oracle; the two agree to fp32 rounding.
+// KeyFormer noise.  Counter-based: element (b, h, query i, key j) of a [B, Hq, M, L] noise field gets
+// 32 hashed bits in three steps so that most of the work is shared along a row or a column:
+//   headkey = mix32(seed_lo ^ mix32(b * Hq + h + seed_hi * 0x9e3779b9))      once per (b, h)
+//   rowhash = mix32(headkey + i * 0x9e3779b9)                                once per query
+//   bits    = fmix(rowhash ^ (j * 0x85ebca6b))                               per element
+// 23 of the bits make u in (0,1) and g = -log(-log(u)) ~ Gumbel(0,1).  The host restatement of this
+// function (same integer steps, float64 logs) lives with the parity oracle.
 // ------------------------------------------------------------------------------------------
 __host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352du;
@@ -85,14 +88,34 @@ __host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x ^= x >> 16;
   return x;
 }
-__host__ __device__ __forceinline__ uint32_t noise_bits(uint64_t seed, uint64_t idx) {
-  uint32_t h = mix32(static_cast<uint32_t>(seed) ^ static_cast<uint32_t>(idx));
-  h ^= static_cast<uint32_t>(idx >> 32) + static_cast<uint32_t>(seed >> 32) * 0x9e3779b9u;
-  return mix32(h + 0x85ebca6bu);
+__host__ __device__ __forceinline__ uint32_t noise_headkey(uint64_t seed, uint32_t bh) {
+  return mix32(static_cast<uint32_t>(seed) ^ mix32(bh + static_cast<uint32_t>(seed >> 32) * 0x9e3779b9u));
 }
+__host__ __device__ __forceinline__ uint32_t noise_rowhash(uint32_t headkey, uint32_t i) {
+  return mix32(headkey + i * 0x9e3779b9u);
+}
+__host__ __device__ __forceinline__ uint32_t noise_elem_bits(uint32_t rowhash, uint32_t j) {
+  uint32_t x = rowhash ^ (j * 0x85ebca6bu);
+  x ^= x >> 16; x *= 0x7feb352du;
+  x ^= x >> 15;
+  return x;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// g = -ln(-ln u), u = (k + 0.5) / 2^23 with k the top 23 bits.  Two MUFU log2 plus a short series for
+// -ln u when u is within 2^-6 of 1 (where log2's absolute error would dominate): relative error of the
+// inner logarithm <= ~1e-5, absolute error of g of the same order.
 __device__ __forceinline__ float gumbel_from_bits(uint32_t bits) {
-  const float u = (static_cast<float>(bits >> 9) + 0.5f) * 1.1920928955078125e-07f;   // 2^-23
-  return -__logf(-logf(u));
+  const uint32_t k = bits >> 9;
+  const float u = (static_cast<float>(k) + 0.5f) * 1.1920928955078125e-07f;                    // 2^-23
+  const float v = (static_cast<float>(0x7fffffu - k) + 0.5f) * 1.1920928955078125e-07f;        // 1 - u, exact
+  const float w_log = -0.6931471805599453f * lg2_approx(u);
+  const float w_ser = v * fmaf(v, fmaf(v, fmaf(v, 0.25f, 0.3333333333f), 0.5f), 1.0f);         // v + v^2/2 + v^3/3 + v^4/4
+  const float w = (v < 0.015625f) ? w_ser : w_log;
+  return -0.6931471805599453f * lg2_approx(w);
 }
 
 struct NoiseSrc {
@@ -100,17 +123,17 @@ struct NoiseSrc {
   const void* ptr;           // tensor mode
   long long sb, sh, si;      // element strides of (b, h, i); j contiguous
   unsigned long long seed;   // gumbel mode
-  long long M, L, Hq;        // field extents for the linear index
+  long long M, L, Hq;        // field extents
 };
 
+// noise of element (b, h, i, j); `rowhash` is noise_rowhash(noise_headkey(seed, b*Hq+h), i)
 template <typename T>
-__device__ __forceinline__ float noise_at(const NoiseSrc& n, int b, int h, int i, int j) {
+__device__ __forceinline__ float noise_at(const NoiseSrc& n, uint32_t rowhash, int b, int h, int i, int j) {
   if (n.mode == TRN_NOISE_TENSOR) {
     const T* p = static_cast<const T*>(n.ptr) + b * n.sb + h * n.sh + i * n.si + j;
     return Io<T>::to_f(*p);
   }
-  const uint64_t idx = ((static_cast<uint64_t>(b) * n.Hq + h) * n.M + i) * n.L + j;
-  return gumbel_from_bits(noise_bits(n.seed, idx));
+  return gumbel_from_bits(noise_elem_bits(rowhash, static_cast<uint32_t>(j)));
 }
 
 }  // namespace trn

@@ -316,6 +316,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     uint32_t r[32];
+    const uint32_t rowhash =
+        (MODE == 1) ? noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)),
+                                    static_cast<uint32_t>(q_abs))
+                    : 0u;
 
     for (int j = 0; j < n_blocks; ++j) {
       const int kv0 = j * BKV;
@@ -337,7 +341,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const int col = kv0 + c * 32 + i;
             float v = -INFINITY;
             if (col <= limit) {
-              const float g = row_valid ? noise_at<T>(p.noise, b, h, q_abs, col) : 0.f;
+              const float g = row_valid ? noise_at<T>(p.noise, rowhash, b, h, q_abs, col) : 0.f;
               v = (__uint_as_float(r[i]) * p.scale + g) * p.pert_log2;
             }
             tv[i] = v;

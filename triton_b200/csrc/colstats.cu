@@ -7,11 +7,16 @@
 // lanes, queries along the columns), so that each thread owns one key and adds its column of
 // probabilities in registers, in a fixed order — no atomics, bitwise reproducible.
 //
-// One CTA = 128 keys of one (batch, query head), looping over the 128-query blocks that can see them:
-//   warp 0     TMA producer: k tile once, q tiles through a 4-stage ring
-//   warp 1     one lane issues tcgen05.mma  S^T = k q^T  into two TMEM buffers
-//   warps 2-5  thread = key: p = 2^(t - lse_query), accumulate sum p and sum p^2
+// One CTA owns TWO 128-key tiles and loops over the 128-query blocks that can see them:
+//   * GQA / MQA: the same keys for two query heads of one kv group (k tile shared through L2, q differs);
+//   * MHA: two consecutive key blocks of one head.
+//   warp 0      TMA producer: both k tiles once, then both tiles' q blocks through a ring
+//   warp 1      one lane issues tcgen05.mma  S^T_t = k_t q_t^T  into two TMEM buffers per tile
+//   warps 2-5   statistics warpgroup of tile 0, warps 6-9 of tile 1; thread = key:
+//               p = 2^(t - lse_query), accumulate sum p and sum p^2 (packed fp32x2 arithmetic)
 #include <math.h>
+
+#include <type_traits>
 
 #include "attn_common.cuh"
 
@@ -20,17 +25,17 @@ namespace {
 
 constexpr int BKEY = 128;
 constexpr int BQRY = 128;
-constexpr int kCsThreads = 192;
-constexpr int kCsStages = 4;
-constexpr int kCsTmemCols = 256;
+constexpr int kCsThreads = 320;
+constexpr int kCsTmemCols = 512;      // tile t, buffer u: columns [(2t+u)*128, +128)
 
 struct CsParams {
   HeadMapInfo qi, ki;
   const float* lse;
   void* sum_p;
   void* sum_p2;
-  int B, M, P, L, Hq, group;
+  int B, M, P, L, Hq, Hkv, group;
   int n_kblocks, n_qblocks;
+  int pair_heads, units;
   int causal;
   int stats_fp32;
   float scale, scale_log2, pert_log2;
@@ -40,14 +45,20 @@ struct CsParams {
 
 template <int D>
 struct CsSmem {
+  static constexpr int kStages = (D == 128) ? 2 : 4;
   static constexpr int kChunks = D / 64;
   static constexpr int kChunkBytes = 128 * 128;
   static constexpr int kTileBytes = kChunks * kChunkBytes;
-  static constexpr int kKOff = 0;
-  static constexpr int kQOff = kTileBytes;
-  static constexpr int kLseOff = kQOff + kCsStages * kTileBytes;    // 4 warps x 2 buffers x 128 floats
-  static constexpr int kBarOff = kLseOff + 4 * 2 * 128 * 4;
+  static constexpr int kKOff = 0;                                     // two k tiles
+  static constexpr int kQOff = 2 * kTileBytes;                        // ring of (q tile 0, q tile 1)
+  static constexpr int kLseOff = kQOff + kStages * 2 * kTileBytes;    // 8 warps x 2 buffers x 128 floats
+  static constexpr int kHashOff = kLseOff + 8 * 2 * 128 * 4;          // same shape: per-query noise row hashes
+  static constexpr int kBarOff = kHashOff + 8 * 2 * 128 * 4;
   static constexpr int kTotal = kBarOff + 256 + 1024;
+};
+
+struct CsTile {
+  int h, kvh, k0, present;
 };
 
 template <typename T, int D, bool PERT>
@@ -55,6 +66,7 @@ __global__ void __launch_bounds__(kCsThreads, 1)
 attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CsParams p) {
   using SM = CsSmem<D>;
+  constexpr int KS = SM::kStages;
   __shared__ int s_skip;
   if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(p.status);
   __syncthreads();
@@ -64,15 +76,16 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bar_base = smem_base + SM::kBarOff;
+  // barriers: k_full, q_full[KS], q_empty[KS], s_full[2 tiles][2 buffers], s_free[2][2]
   const uint32_t k_full = bar_base;
   auto q_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto q_empty = [&](int s) { return bar_base + 8u * (1 + kCsStages + s); };
-  auto s_full = [&](int b) { return bar_base + 8u * (1 + 2 * kCsStages + b); };
-  auto s_free = [&](int b) { return bar_base + 8u * (3 + 2 * kCsStages + b); };
-  volatile uint32_t* tmem_ptr_smem =
-      reinterpret_cast<volatile uint32_t*>(smem_gen + SM::kBarOff + 8 * (5 + 2 * kCsStages));
+  auto q_empty = [&](int s) { return bar_base + 8u * (1 + KS + s); };
+  auto s_full = [&](int t, int u) { return bar_base + 8u * (1 + 2 * KS + 2 * t + u); };
+  auto s_free = [&](int t, int u) { return bar_base + 8u * (5 + 2 * KS + 2 * t + u); };
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + SM::kBarOff + 8 * (9 + 2 * KS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   float* lse_s = reinterpret_cast<float*>(smem_gen + SM::kLseOff);
+  uint32_t* hash_s = reinterpret_cast<uint32_t*>(smem_gen + SM::kHashOff);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -80,14 +93,15 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(k_full, 1);
-    for (int s = 0; s < kCsStages; ++s) {
+    for (int s = 0; s < KS; ++s) {
       mbar_init(q_full(s), 1);
       mbar_init(q_empty(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full(b), 1);
-      mbar_init(s_free(b), 128);
-    }
+    for (int t = 0; t < 2; ++t)
+      for (int u = 0; u < 2; ++u) {
+        mbar_init(s_full(t, u), 1);
+        mbar_init(s_free(t, u), 128);
+      }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -100,42 +114,65 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  // ---- which tile: early key blocks (seen by the most queries under a causal mask) first
-  const int nbh = p.B * p.Hq;
-  const int kb = static_cast<int>(blockIdx.x) / nbh;
-  const int bh = static_cast<int>(blockIdx.x) % nbh;
-  const int b = bh / p.Hq;
-  const int h = bh - b * p.Hq;
-  const int kvh = h / p.group;
-  const int k0 = kb * BKEY;
-  // first query block that can see any key of this tile: query q sees key k iff k <= P + q
-  const int i_start = p.causal ? max(0, k0 - p.P) / BQRY : 0;
+  // ---- which two tiles: early key blocks (seen by the most queries under a causal mask) first
+  const int row_blk = static_cast<int>(blockIdx.x) / p.units;
+  const int unit = static_cast<int>(blockIdx.x) % p.units;
+  int b;
+  CsTile tile[2];
+  if (p.pair_heads) {
+    const int pairs_per_group = (p.group + 1) >> 1;
+    const int pi = unit % pairs_per_group;
+    const int bk = unit / pairs_per_group;
+    const int kvh = bk % p.Hkv;
+    b = bk / p.Hkv;
+    tile[0] = CsTile{kvh * p.group + 2 * pi, kvh, row_blk * BKEY, 1};
+    tile[1] = CsTile{kvh * p.group + 2 * pi + 1, kvh, row_blk * BKEY, (2 * pi + 1 < p.group) ? 1 : 0};
+  } else {
+    b = unit / p.Hq;
+    const int h = unit - b * p.Hq;
+    const int kvh = h / p.group;
+    tile[0] = CsTile{h, kvh, row_blk * 2 * BKEY, 1};
+    tile[1] = CsTile{h, kvh, row_blk * 2 * BKEY + BKEY, (row_blk * 2 * BKEY + BKEY < p.L) ? 1 : 0};
+  }
+  // first query block that can see any key of tile 0 (tile 1 starts at or after it): query q sees key k
+  // iff k <= P + q
+  const int i_start = p.causal ? max(0, tile[0].k0 - p.P) / BQRY : 0;
   const int n_iter = p.n_qblocks - i_start;
 
-  const uint32_t k_s = smem_base + SM::kKOff;
-  auto q_s = [&](int s) { return smem_base + SM::kQOff + s * SM::kTileBytes; };
+  auto k_s = [&](int t) { return smem_base + SM::kKOff + t * SM::kTileBytes; };
+  auto q_s = [&](int s, int t) { return smem_base + SM::kQOff + (s * 2 + t) * SM::kTileBytes; };
 
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
-      mbar_expect_tx(k_full, SM::kTileBytes);
+      const int n_tiles = tile[0].present + tile[1].present;
+      mbar_expect_tx(k_full, n_tiles * SM::kTileBytes);
 #pragma unroll
-      for (int c = 0; c < SM::kChunks; ++c)
-        tma_load_head_tile(k_s + c * SM::kChunkBytes, &tm_k, k_full, p.ki, c * 64, k0, kvh, b);
+      for (int t = 0; t < 2; ++t)
+        if (tile[t].present) {
+#pragma unroll
+          for (int c = 0; c < SM::kChunks; ++c)
+            tma_load_head_tile(k_s(t) + c * SM::kChunkBytes, &tm_k, k_full, p.ki, c * 64, tile[t].k0, tile[t].kvh, b);
+        }
     }
     for (int it = 0; it < n_iter; ++it) {
-      const int st = it % kCsStages;
-      const uint32_t ph = (it / kCsStages) & 1;
+      const int st = it % KS;
+      const uint32_t ph = (it / KS) & 1;
       bool ok = mbar_wait(q_empty(st), ph ^ 1u, ctl, KST_TIMEOUT_PRODUCER);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (lane == 0) {
-        mbar_expect_tx(q_full(st), SM::kTileBytes);
+        const int n_tiles = tile[0].present + tile[1].present;
+        mbar_expect_tx(q_full(st), n_tiles * SM::kTileBytes);
 #pragma unroll
-        for (int c = 0; c < SM::kChunks; ++c)
-          tma_load_head_tile(q_s(st) + c * SM::kChunkBytes, &tm_q, q_full(st), p.qi, c * 64, (i_start + it) * BQRY,
-                             h, b);
+        for (int t = 0; t < 2; ++t)
+          if (tile[t].present) {
+#pragma unroll
+            for (int c = 0; c < SM::kChunks; ++c)
+              tma_load_head_tile(q_s(st, t) + c * SM::kChunkBytes, &tm_q, q_full(st), p.qi, c * 64,
+                                 (i_start + it) * BQRY, tile[t].h, b);
+          }
       }
       __syncwarp();
     }
@@ -144,90 +181,128 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     bool ok = mbar_wait(k_full, 0, ctl, KST_TIMEOUT_MMA);
     ok = __all_sync(0xffffffffu, ok);
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int st = it % kCsStages;
-      const uint32_t ph = (it / kCsStages) & 1;
-      bool w = mbar_wait(q_full(st), ph, ctl, KST_TIMEOUT_MMA);
-      w = w && mbar_wait(s_free(it & 1), ((it >> 1) & 1) ^ 1u, ctl, KST_TIMEOUT_MMA);
-      ok = __all_sync(0xffffffffu, w);
+      const int st = it % KS;
+      const uint32_t ph = (it / KS) & 1;
+      const int u = it & 1;
+      ok = mbar_wait(q_full(st), ph, ctl, KST_TIMEOUT_MMA);
+      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t d_tmem = tmem_base + (it & 1) * BQRY;
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (!tile[t].present) continue;
+        ok = mbar_wait(s_free(t, u), ((it >> 1) & 1) ^ 1u, ctl, KST_TIMEOUT_MMA);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t d_tmem = tmem_base + (2 * t + u) * BQRY;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * SM::kChunkBytes + (kk & 3) * 32;
-          umma_ss(d_tmem, make_smem_desc(k_s + off, 0, 1024), make_smem_desc(q_s(st) + off, 0, 1024), idesc,
-                  kk != 0 ? 1u : 0u);
-        }
-        umma_commit(q_empty(st));
-        umma_commit(s_full(it & 1));
-      }
-      __syncwarp();
-    }
-  } else {
-    const int quad = warp & 3;
-    const int row = quad * 32 + lane;            // key within the tile
-    const int key = k0 + row;
-    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    float acc1 = 0.f, acc2 = 0.f;
-    bool ok = true;
-    uint32_t r[32];
-    for (int it = 0; it < n_iter; ++it) {
-      const int sb = it & 1;
-      const int q0 = (i_start + it) * BQRY;
-      {
-        // each warp stages its own copy of this block's per-query log-sum-exp (no cross-warp barrier);
-        // +inf for queries past M makes their p = 0
-        float* dst = lse_s + (quad * 2 + sb) * 128;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int q = q0 + u * 32 + lane;
-          float v = INFINITY;
-          if (q < p.M) v = __ldg(p.lse + (static_cast<long long>(b) * p.Hq + h) * p.M + q);
-          dst[u * 32 + lane] = v;
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * SM::kChunkBytes + (kk & 3) * 32;
+            umma_ss(d_tmem, make_smem_desc(k_s(t) + off, 0, 1024), make_smem_desc(q_s(st, t) + off, 0, 1024), idesc,
+                    kk != 0 ? 1u : 0u);
+          }
+          umma_commit(s_full(t, u));
         }
         __syncwarp();
       }
-      ok = mbar_wait(s_full(sb), (it >> 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
+      if (!ok) break;
+      if (lane == 0) umma_commit(q_empty(st));
+      __syncwarp();
+    }
+  } else {
+    const int t = (warp - 2) >> 2;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;            // key within the tile
+    const int key = tile[t].k0 + row;
+    const int h = tile[t].h;
+    const bool present = tile[t].present != 0;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    float* my_lse = lse_s + ((warp - 2) * 2) * 128;
+    uint32_t* my_hash = hash_s + ((warp - 2) * 2) * 128;
+    const uint32_t headkey = PERT ? noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)) : 0u;
+    float2 acc1 = make_float2(0.f, 0.f), acc2 = make_float2(0.f, 0.f);
+    bool ok = true;
+    uint32_t r[32];
+    const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+    for (int it = 0; it < n_iter && present; ++it) {
+      const int u = it & 1;
+      const int q0 = (i_start + it) * BQRY;
+      float* nl = my_lse + u * 128;
+      {
+        // each warp stages its own copy of this block's per-query NEGATED log-sum-exp (no cross-warp
+        // barrier); -inf for queries past M makes their p = 0
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int q = q0 + v * 32 + lane;
+          float val = -INFINITY;
+          if (q < p.M) val = -__ldg(p.lse + (static_cast<long long>(b) * p.Hq + h) * p.M + q);
+          nl[v * 32 + lane] = val;
+          if (PERT) my_hash[u * 128 + v * 32 + lane] = noise_rowhash(headkey, static_cast<uint32_t>(q));
+        }
+        __syncwarp();
+      }
+      ok = mbar_wait(s_full(t, u), (it >> 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_tmem = tmem_base + sb * BQRY + lane_addr;
+      const uint32_t s_tmem = tmem_base + (2 * t + u) * BQRY + lane_addr;
       // causal: this key is visible to query q0 + col iff col >= key - P - q0
       const int cmin = p.causal ? (key - p.P - q0) : 0;
-      const bool masked = p.causal && (k0 + BKEY - 1 - p.P > q0);
-      const float* lrow = lse_s + (quad * 2 + sb) * 128;
-      for (int c = 0; c < BQRY / 32; ++c) {
-        tmem_ld32(s_tmem + c * 32, r);
-        tmem_wait_ld();
+      const bool masked = p.causal && (tile[t].k0 + BKEY - 1 - p.P > q0);
+      if (PERT || masked) {
+        for (int c = 0; c < BQRY / 32; ++c) {
+          tmem_ld32(s_tmem + c * 32, r);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c * 32 + i;
-          float t;
-          if (PERT) {
-            const int q = q0 + col;
-            const float g = (q < p.M && key < p.L) ? noise_at<T>(p.noise, b, h, q, key) : 0.f;
-            t = (__uint_as_float(r[i]) * p.scale + g) * p.pert_log2;
-          } else {
-            t = __uint_as_float(r[i]) * p.scale_log2;
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            float tt;
+            if (PERT) {
+              const int q = q0 + col;
+              const float g = (q < p.M && key < p.L) ? noise_at<T>(p.noise, my_hash[u * 128 + col], b, h, q, key) : 0.f;
+              tt = (__uint_as_float(r[i]) * p.scale + g) * p.pert_log2;
+            } else {
+              tt = __uint_as_float(r[i]) * p.scale_log2;
+            }
+            float pr = ex2_approx(tt + nl[col]);
+            if (masked && col < cmin) pr = 0.f;
+            acc1.x += pr;
+            acc2.x = fmaf(pr, pr, acc2.x);
           }
-          float pr = ex2_approx(t - lrow[col]);
-          if (masked && col < cmin) pr = 0.f;
-          acc1 += pr;
-          acc2 = fmaf(pr, pr, acc2);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BQRY / 32; ++c) {
+          tmem_ld32(s_tmem + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 n4 = *reinterpret_cast<const float4*>(nl + c * 32 + i);
+            const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2,
+                                         make_float2(n4.x, n4.y));
+            const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), c2,
+                                         make_float2(n4.z, n4.w));
+            const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+            const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+            acc1 = __fadd2_rn(acc1, p0);
+            acc2 = __ffma2_rn(p0, p0, acc2);
+            acc1 = __fadd2_rn(acc1, p1);
+            acc2 = __ffma2_rn(p1, p1, acc2);
+          }
         }
       }
       tc_fence_before();
-      mbar_arrive(s_free(sb));
+      mbar_arrive(s_free(t, u));
     }
-    if (ok && key < p.L) {
+    if (ok && present && key < p.L) {
+      const float a1 = acc1.x + acc1.y, a2 = acc2.x + acc2.y;
       const long long o = (static_cast<long long>(b) * p.Hq + h) * p.L + key;
       if (p.stats_fp32) {
-        static_cast<float*>(p.sum_p)[o] = acc1;
-        if (p.sum_p2 != nullptr) static_cast<float*>(p.sum_p2)[o] = acc2;
+        static_cast<float*>(p.sum_p)[o] = a1;
+        if (p.sum_p2 != nullptr) static_cast<float*>(p.sum_p2)[o] = a2;
       } else {
-        static_cast<T*>(p.sum_p)[o] = Io<T>::from_f(acc1);
-        if (p.sum_p2 != nullptr) static_cast<T*>(p.sum_p2)[o] = Io<T>::from_f(acc2);
+        static_cast<T*>(p.sum_p)[o] = Io<T>::from_f(a1);
+        if (p.sum_p2 != nullptr) static_cast<T*>(p.sum_p2)[o] = Io<T>::from_f(a2);
       }
     }
   }
@@ -257,9 +332,18 @@ int launch_inst(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds
   p.lse = a.lse;
   p.sum_p = a.sum_p;
   p.sum_p2 = a.sum_p2;
-  p.B = a.B; p.M = a.M; p.P = a.P; p.L = L; p.Hq = a.Hq; p.group = a.Hq / a.Hkv;
+  p.B = a.B; p.M = a.M; p.P = a.P; p.L = L; p.Hq = a.Hq; p.Hkv = a.Hkv; p.group = a.Hq / a.Hkv;
   p.n_kblocks = (L + BKEY - 1) / BKEY;
   p.n_qblocks = (a.M + BQRY - 1) / BQRY;
+  p.pair_heads = p.group >= 2 ? 1 : 0;
+  long long rows_of_ctas;
+  if (p.pair_heads) {
+    p.units = a.B * a.Hkv * ((p.group + 1) / 2);
+    rows_of_ctas = p.n_kblocks;
+  } else {
+    p.units = a.B * a.Hq;
+    rows_of_ctas = (p.n_kblocks + 1) / 2;
+  }
   p.causal = a.causal;
   p.stats_fp32 = a.stats_fp32;
   p.scale = a.scale;
@@ -274,7 +358,7 @@ int launch_inst(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds
   auto kern = attn_colstats_kernel<T, D, PERT>;
   rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
   if (rc != TRN_OK) return rc;
-  const long long grid = static_cast<long long>(p.n_kblocks) * a.B * a.Hq;
+  const long long grid = rows_of_ctas * p.units;
   if (grid > 0x7fffffffLL) return TRN_E_SHAPE;
   kern<<<static_cast<int>(grid), kCsThreads, SM::kTotal, st>>>(tm_q, tm_k, p);
   TRN_CUDA_TRY(cudaGetLastError());
