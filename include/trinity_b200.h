@@ -190,6 +190,14 @@ typedef struct {
 int trinity_topk(const TrnTopkArgs* a, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * fp32 <-> 16-bit conversion of n contiguous elements (n a multiple of 8): to_fp32 = 0 rounds fp32 `src`
+ * to `dtype16` in `dst`, to_fp32 = 1 widens.  For fp32 callers (the fp32 Vanilla configuration; the
+ * reference's own tensors are fp16, convert_eval_rms.py:24): the kernels compute on 16-bit operands with
+ * fp32 accumulation.
+ * ---------------------------------------------------------------------------------------------- */
+int trinity_convert(const void* src, void* dst, int64_t n, int dtype16, int to_fp32, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Whole block, the unit the reference's generated forward() computes (TritonGen.py:590-708):
  *   [PreNorm row statistics] -> QKV projection (+QKNorm, +cache append) -> attention ->
  *   [KeyFormer / RoCo per-key statistics].

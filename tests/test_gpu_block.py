@@ -202,3 +202,31 @@ def test_block_argument_validation():
     with pytest.raises(L.TrinityError):
         run_block("keyformer", t, B=1, M=16, P=0, Hq=2, Hkv=2, D=64, causal=False, scale=1.0, noise_mode=L.TRN_NOISE_TENSOR)
     assert L.kernel_status() == 0
+
+
+def test_fp32_vanilla_configuration():
+    """The fp32 Vanilla Llama3-8B configuration (X[1,512,4096] ~ N(0,1), Wq 4096x4096, Wk/Wv 4096x1024 ~ N(0,1/4096),
+    32 query / 8 kv heads of 128, causal softmax(q k^T / sqrt(128)) v, seed 0) through the drop-in path with fp32
+    tensors.  The kernels compute on bf16-rounded operands with fp32 accumulation, so this is an end-to-end
+    comparison (abs <= 2e-2; rel <= 5e-2 above 10 % of max|ref|) against the fp32 oracle on the fp32 inputs."""
+    consts = {"M": 512, "N": 4096, "D": 128, "H": 32, "P": 0, "HKV": 8, "CAUSAL": 1, "SCALE_RSQRT_D": 1}
+    shapes = dict(SHAPE_DICT)
+    shapes["WK"] = ("N", 1024)
+    shapes["WV"] = ("N", 1024)
+    shapes["K_cache"] = (8, "P+M", "D")
+    shapes["V_cache"] = (8, "P+M", "D")
+    src = convert_ir_to_triton(open(IR_DIR / "vanilla.txt").read(), shapes, consts)
+    mod = _load_generated(src, "gen_cfg1")
+    torch.manual_seed(0)
+    host = {"X": torch.randn(512, 4096), "WQ": torch.randn(4096, 4096) / 64, "WK": torch.randn(4096, 1024) / 64,
+            "WV": torch.randn(4096, 1024) / 64, "K_cache": torch.zeros(8, 512, 128), "V_cache": torch.zeros(8, 512, 128),
+            "Q": torch.zeros(32, 512, 128), "O2": torch.zeros(512, 4096)}
+    T = {k: v.cuda() for k, v in host.items()}
+    mod.forward(*[T[p] for p in mod.TENSOR_PARAMS])
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0 and T["O2"].dtype == torch.float32
+    r = O.attn_block("vanilla", X=host["X"], Wq=host["WQ"], Wk=host["WK"], Wv=host["WV"], B=1, M=512, P=0, Hq=32, Hkv=8,
+                     D=128, causal=True, scale=128 ** -0.5)
+    assert_parity(T["O2"].view(512, 32, 128), r["out_bmhd"][0], "fp32 vanilla out", rel_floor=REL_FLOOR_FP32,
+                  rel_tol=REL_TOL_E2E)
+    assert_parity(T["K_cache"], r["k_all"][0], "fp32 vanilla k", rel_floor=REL_FLOOR_FP32, rel_tol=REL_TOL_E2E)

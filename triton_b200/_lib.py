@@ -27,7 +27,7 @@ EXPORTS = (
     "trinity_abi_version", "trinity_strerror", "trinity_last_cuda_error", "trinity_last_kernel_status",
     "trinity_rmsnorm", "trinity_qkv_project", "trinity_attention", "trinity_attn_colstats", "trinity_topk",
     "trinity_attn_block_workspace", "trinity_attn_block", "trinity_attn_block_host",
-    "trinity_static_scratch_capacity", "trinity_attn_block_static",
+    "trinity_static_scratch_capacity", "trinity_attn_block_static", "trinity_convert",
 )
 
 
@@ -145,6 +145,8 @@ def load() -> C.CDLL:
         fn.argtypes = [C.POINTER(typ), C.c_void_p]
     lib.trinity_attn_block_workspace.restype = C.c_size_t
     lib.trinity_attn_block_workspace.argtypes = [C.POINTER(TrnBlockArgs)]
+    lib.trinity_convert.restype = C.c_int
+    lib.trinity_convert.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]
     lib.trinity_static_scratch_capacity.restype = C.c_size_t
     lib.trinity_static_scratch_capacity.argtypes = []
     if lib.trinity_abi_version() != ABI_VERSION:

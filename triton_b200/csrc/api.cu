@@ -223,6 +223,13 @@ int trinity_topk(const TrnTopkArgs* a, void* cuda_stream) {
   return launch_topk(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
 }
 
+int trinity_convert(const void* src, void* dst, int64_t n, int dtype16, int to_fp32, void* cuda_stream) {
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  return launch_convert(src, dst, n, dtype16, to_fp32, static_cast<cudaStream_t>(cuda_stream), *ds);
+}
+
 size_t trinity_attn_block_workspace(const TrnBlockArgs* a) {
   if (a == nullptr || a->B <= 0 || a->M <= 0 || a->Hq <= 0) return 0;
   return block_workspace_layout(*a).total;

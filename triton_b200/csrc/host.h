@@ -50,5 +50,7 @@ int launch_qkv_project(const TrnProjArgs& a, cudaStream_t st, const DeviceState&
 int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_colstats(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_topk(const TrnTopkArgs& a, cudaStream_t st, const DeviceState& ds);
+int launch_convert(const void* src, void* dst, long long n, int dtype16, int to_fp32, cudaStream_t st,
+                   const DeviceState& ds);
 
 }  // namespace trn

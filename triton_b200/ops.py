@@ -231,5 +231,20 @@ class BlockPlan:
         L.check(self._lib.trinity_attn_block(C.byref(self.args), _stream()))
 
 
+def convert(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    """fp32 -> bf16/fp16 (rounding) or bf16/fp16 -> fp32 (widening) of contiguous tensors of equal numel."""
+    _need_cuda(src, dst)
+    if not (src.is_contiguous() and dst.is_contiguous()) or src.numel() != dst.numel():
+        raise ValueError("convert needs contiguous tensors of equal size")
+    if src.dtype == torch.float32 and dst.dtype in _DTYPES:
+        code, to32 = _DTYPES[dst.dtype], 0
+    elif dst.dtype == torch.float32 and src.dtype in _DTYPES:
+        code, to32 = _DTYPES[src.dtype], 1
+    else:
+        raise TypeError(f"convert: unsupported pair {src.dtype} -> {dst.dtype}")
+    L.check(L.load().trinity_convert(src.data_ptr(), dst.data_ptr(), src.numel(), code, to32, _stream()))
+    return dst
+
+
 def default_scale(D: int) -> float:
     return 1.0 / math.sqrt(D)

@@ -59,7 +59,7 @@ class BoundOperator:
             t2 = self._batched(t, 2)
             return t2.view(t2.shape[0], t2.shape[1], -1, self.D)
         t3 = self._batched(t, 3)
-        if sym[0] == "H":                     # ('H', rows, 'D'): head-major
+        if sym[0] == "H" or sym[1] in ("M", "P+M", "P"):      # (heads, rows, 'D'): head-major
             return t3.permute(0, 2, 1, 3)
         return t3                             # ('M', 'H', 'D'): token-major
 
@@ -100,14 +100,37 @@ class BoundOperator:
             kw.update(sum_p=t["C_out1"], sum_p2=t["C_out2"])
         return ("block", ops.BlockPlan(self.variant, **kw))
 
+    _INPUTS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise", "gamma", "gamma_q", "gamma_k")
+    _OUTPUTS = ("O2", "O1", "O", "Q", "Q_norm", "K_cache", "V_cache", "C_out", "C_out1", "C_out2", "X_norm")
+
+    def _bind_any(self, tensors: Sequence[torch.Tensor]):
+        """fp32 callers (the fp32 Vanilla configuration): 16-bit shadows of every tensor are allocated at
+        bind time; each call rounds the inputs into them, runs the 16-bit kernels (fp32 accumulation) and
+        widens the outputs back.  16-bit callers bind directly."""
+        if not any(isinstance(v, torch.Tensor) and v.dtype == torch.float32 for v in tensors):
+            return self._bind(tensors), (), ()
+        shadow_dt = torch.bfloat16
+        shadows = [torch.empty(v.shape, dtype=shadow_dt, device=v.device) if v.dtype == torch.float32 else v
+                   for v in tensors]
+        pairs_in = tuple((v, sh) for n, v, sh in zip(self.names, tensors, shadows)
+                         if v.dtype == torch.float32 and n in self._INPUTS)
+        pairs_out = tuple((sh, v) for n, v, sh in zip(self.names, tensors, shadows)
+                          if v.dtype == torch.float32 and n in self._OUTPUTS)
+        return self._bind(shadows), pairs_in, pairs_out
+
     def __call__(self, tensors: Sequence[torch.Tensor]) -> None:
         key = tuple(int(v.data_ptr()) for v in tensors)
-        plan = self._plans.get(key)
-        if plan is None:
-            plan = self._bind(tensors)
-            self._plans[key] = plan
+        bound = self._plans.get(key)
+        if bound is None:
+            bound = self._bind_any(tensors)
+            self._plans[key] = bound
+        plan, pairs_in, pairs_out = bound
+        for src, dst in pairs_in:
+            ops.convert(src.contiguous(), dst)
         if plan[0] == "rms":
             _, x, y, gamma, x2 = plan
             ops.rmsnorm(x, gamma, self.eps, out=y)
         else:
             plan[1].run()
+        for src, dst in pairs_out:
+            ops.convert(src, dst)
