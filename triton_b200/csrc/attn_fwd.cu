@@ -221,11 +221,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (lane == 0) {
         const int st = j % KS;
         const uint32_t d_tmem = tmem_base + t * BKV;
+        // descriptors are built once per block and advanced by constants (the address field counts 16 bytes)
+        const uint64_t qd = make_smem_desc(q_s(t), 0, 1024);
+        const uint64_t kd = make_smem_desc(k_s(st), 0, 1024);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * SM::kChunkBytes + (kk & 3) * 32;
-          umma_ss(d_tmem, make_smem_desc(q_s(t) + off, 0, 1024), make_smem_desc(k_s(st) + off, 0, 1024), idesc_qk,
-                  kk != 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>(((kk >> 2) * SM::kChunkBytes + (kk & 3) * 32) >> 4);
+          umma_ss(d_tmem, qd + off, kd + off, idesc_qk, kk != 0 ? 1u : 0u);
         }
         umma_commit(s_full(t));
       }
@@ -252,6 +254,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (!ok) break;
           const uint32_t o_tmem = tmem_base + 2 * BKV + t * BKV;
           const uint32_t p_tmem = tmem_base + t * BKV;
+          const uint64_t vd = make_smem_desc(v_s(st), SM::kChunkBytes, 1024);
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             // first / second 64 keys of P_t(j) are in TMEM
@@ -266,7 +269,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               for (int k4 = 0; k4 < BKV / 32; ++k4) {
                 const int kk = half * (BKV / 32) + k4;
                 const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
-                const uint64_t bdesc = make_smem_desc(v_s(st) + kk * 2048, SM::kChunkBytes, 1024);
+                const uint64_t bdesc = vd + static_cast<uint64_t>((kk * 2048) >> 4);
                 umma_ts(o_tmem, p_tmem + a_col, bdesc, idesc_pv, (j | kk) != 0 ? 1u : 0u);
                 if constexpr (SPLIT) umma_ts(o_tmem, p_tmem + a_col + 16, bdesc, idesc_pv, 1u);
               }
