@@ -118,6 +118,17 @@ __device__ __forceinline__ float gumbel_from_bits(uint32_t bits) {
   return -0.6931471805599453f * lg2_approx(w);
 }
 
+// log2 of E = -ln u for the same u: the Gumbel value is g = -ln2 * log2(E), so callers that work in the
+// log2 domain fold the constant into their own scale
+__device__ __forceinline__ float gumbel_log2e_from_bits(uint32_t bits) {
+  const uint32_t k = bits >> 9;
+  const float u = fmaf(static_cast<float>(k), 1.1920928955078125e-07f, 5.9604644775390625e-08f);
+  const float v = fmaf(static_cast<float>(0x7fffffu - k), 1.1920928955078125e-07f, 5.9604644775390625e-08f);
+  const float w_log = -0.6931471805599453f * lg2_approx(u);
+  const float w_ser = v * fmaf(v, fmaf(v, fmaf(v, 0.25f, 0.3333333333f), 0.5f), 1.0f);
+  return lg2_approx((v < 0.015625f) ? w_ser : w_log);
+}
+
 struct NoiseSrc {
   int mode;                  // TRN_NOISE_*
   const void* ptr;           // tensor mode

@@ -334,11 +334,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       if (MODE == 1) {
         // one pass, chunk-wise online log-sum-exp of the perturbed scores
+        const bool fast = !masked && p.noise.mode == TRN_NOISE_GUMBEL;
+        // t = (s * scale + g) * log2(e) / tau with g = -ln2 * log2(E):  t = s * c_s + log2(E) * c_g
+        const float c_s = p.scale * p.pert_log2;
+        const float c_g = -0.6931471805599453f * p.pert_log2;
         for (int c = 0; c < BKV / 32; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
           float tv[32];
           float cm = -INFINITY;
+          if (fast) {
+            // interior block, generated noise: no per-element compare, hash advanced by one add per key
+            uint32_t jc = static_cast<uint32_t>(kv0 + c * 32) * 0x85ebca6bu;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              uint32_t x = rowhash ^ jc;
+              jc += 0x85ebca6bu;
+              x ^= x >> 16; x *= 0x7feb352du;
+              x ^= x >> 15;
+              const float v = fmaf(gumbel_log2e_from_bits(x), c_g, __uint_as_float(r[i]) * c_s);
+              tv[i] = v;
+              cm = fmaxf(cm, v);
+            }
+          } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = kv0 + c * 32 + i;
@@ -349,6 +367,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             tv[i] = v;
             cm = fmaxf(cm, v);
+          }
           }
           const float m_new = fmaxf(m_run, cm);
           if (m_new != -INFINITY) {

@@ -249,7 +249,35 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // causal: this key is visible to query q0 + col iff col >= key - P - q0
       const int cmin = p.causal ? (key - p.P - q0) : 0;
       const bool masked = p.causal && (tile[t].k0 + BKEY - 1 - p.P > q0);
-      if (PERT || masked) {
+      if (PERT && !masked && p.noise.mode == TRN_NOISE_GUMBEL) {   // warp-uniform: rows past L just compute unused values
+        // interior block, generated noise: the per-key part of the hash is a thread constant, the
+        // per-query part comes from shared memory four at a time
+        const uint32_t jc = static_cast<uint32_t>(key) * 0x85ebca6bu;
+        const float c_s = p.scale * p.pert_log2;
+        const float c_g = -0.6931471805599453f * p.pert_log2;
+        const uint32_t* hrow = my_hash + u * 128;
+#pragma unroll 1
+        for (int c = 0; c < BQRY / 32; ++c) {
+          tmem_ld32(s_tmem + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const uint4 h4 = *reinterpret_cast<const uint4*>(hrow + c * 32 + i);
+            const float4 n4 = *reinterpret_cast<const float4*>(nl + c * 32 + i);
+            const uint32_t hh[4] = {h4.x, h4.y, h4.z, h4.w};
+            const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              uint32_t x = hh[e] ^ jc;
+              x ^= x >> 16; x *= 0x7feb352du;
+              x ^= x >> 15;
+              const float tt = fmaf(gumbel_log2e_from_bits(x), c_g, fmaf(__uint_as_float(r[i + e]), c_s, nn[e]));
+              const float pr = ex2_approx(tt);
+              if (e & 1) acc1.y += pr; else acc1.x += pr;
+            }
+          }
+        }
+      } else if (PERT || masked) {
         for (int c = 0; c < BQRY / 32; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
