@@ -52,6 +52,7 @@ struct AttnParams {
   float scale_log2;    // MODE 0: scale * log2(e)
   float pert_log2;     // MODE 1: log2(e) / tau
   NoiseSrc noise;
+  int noise_vec_ok;    // noise tensor base and strides allow 128-bit row loads
   int* status;
 };
 
@@ -335,6 +336,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (MODE == 1) {
         // one pass, chunk-wise online log-sum-exp of the perturbed scores
         const bool fast = !masked && p.noise.mode == TRN_NOISE_GUMBEL;
+        // 128-bit loads need the noise rows 16-byte aligned (checked once on the host)
+        const bool fast_tensor = !masked && p.noise.mode == TRN_NOISE_TENSOR && p.noise_vec_ok;
         // t = (s * scale + g) * log2(e) / tau with g = -ln2 * log2(E):  t = s * c_s + log2(E) * c_g
         const float c_s = p.scale * p.pert_log2;
         const float c_g = -0.6931471805599453f * p.pert_log2;
@@ -355,6 +358,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               const float v = fmaf(gumbel_log2e_from_bits(x), c_g, __uint_as_float(r[i]) * c_s);
               tv[i] = v;
               cm = fmaxf(cm, v);
+            }
+          } else if (fast_tensor) {
+            // interior block, noise tensor: this row's 32 values come in as four 128-bit loads
+            const T* nrow = static_cast<const T*>(p.noise.ptr) + b * p.noise.sb + h * p.noise.sh +
+                            static_cast<long long>(row_valid ? q_abs : 0) * p.noise.si + kv0 + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              const uint4 nv = __ldg(reinterpret_cast<const uint4*>(nrow + i));
+              const uint32_t w4[4] = {nv.x, nv.y, nv.z, nv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 g2 = Io<T>::unpack2(w4[e]);
+                const float v0 = (__uint_as_float(r[i + 2 * e]) * p.scale + g2.x) * p.pert_log2;
+                const float v1 = (__uint_as_float(r[i + 2 * e + 1]) * p.scale + g2.y) * p.pert_log2;
+                tv[i + 2 * e] = v0;
+                tv[i + 2 * e + 1] = v1;
+                cm = fmax3(cm, v0, v1);
+              }
             }
           } else {
 #pragma unroll
@@ -566,6 +587,10 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   p.noise.sb = a.noise_stride_b; p.noise.sh = a.noise_stride_h; p.noise.si = a.noise_stride_i;
   p.noise.seed = a.seed;
   p.noise.M = a.M; p.noise.L = L; p.noise.Hq = a.Hq;
+  p.noise_vec_ok = (a.noise != nullptr && aligned16(a.noise) && (a.noise_stride_b & 7) == 0 &&
+                    (a.noise_stride_h & 7) == 0 && (a.noise_stride_i & 7) == 0)
+                       ? 1
+                       : 0;
   p.status = ds.status;
   auto kern = attn_fwd_kernel<T, D, MODE, SPLIT>;
   rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
