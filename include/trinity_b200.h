@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define TRINITY_ABI_VERSION 1
+#define TRINITY_ABI_VERSION 2
 
 /* element types of activations / weights / outputs */
 enum { TRN_BF16 = 0, TRN_FP16 = 1 };
@@ -144,8 +144,16 @@ typedef struct {
   uint64_t seed;
   int single_p;          /* 0 (default): p is carried as hi + lo 16-bit parts into the P v product;
                             1: one 16-bit part only (faster, ~8 / 11 mantissa bits of p)            */
+  void* workspace;       /* optional device scratch, 256-byte aligned (NULL: none).  With it, a launch that
+                            would fill less than half of the SMs divides each tile's key range among several
+                            CTAs (split-KV) and merges their partial results with a second small kernel; the
+                            result is the same softmax.  Contents need not be initialised.               */
+  size_t workspace_bytes; /* a smaller area than trinity_attention_workspace() asks for means fewer splits */
 } TrnAttnArgs;
 int trinity_attention(const TrnAttnArgs* a, void* cuda_stream);
+/* Scratch that makes split-KV possible for this shape (0: the launch would not split).  No reference
+ * counterpart: the generated Triton kernels never split the key loop (TritonGen.py:3071 walks it whole). */
+size_t trinity_attention_workspace(const TrnAttnArgs* a);
 
 /* ------------------------------------------------------------------------------------------------
  * Per-key statistics over queries (RoCo ref_rms.py:274-275, KeyFormer's C_out,

@@ -135,6 +135,47 @@ def test_attention_core(B, M, P, Hq, Hkv, D, dt, causal, scale):
     assert (lse.cpu() - lref).abs().max().item() <= 1e-4
 
 
+SPLIT_CASES = [
+    # B, M, P, Hq, Hkv, D, dtype, causal: launches that fill less than half of the SMs
+    (1, 16, 1024, 32, 32, 128, HF, False),            # the reference's chunked-prefill shape: 4 splits
+    (1, 16, 1024, 8, 2, 128, BF, True),               # GQA head pairs, 8 splits
+    (1, 200, 900, 4, 4, 64, BF, True),                # MHA: two query blocks of unequal length per CTA
+    (2, 1, 2047, 6, 3, 64, HF, True),                 # decode: one query, ragged last key block
+    (1, 300, 1500, 3, 1, 128, BF, True),              # MQA, odd group: a CTA with a single tile
+]
+
+
+@pytest.mark.parametrize("B,M,P,Hq,Hkv,D,dt,causal", SPLIT_CASES)
+def test_attention_split_kv_matches_unsplit_and_oracle(B, M, P, Hq, Hkv, D, dt, causal):
+    scale = D ** -0.5
+    q, kc, vc = _attn_inputs(B, M, P, Hq, Hkv, D, dt, seed=11)
+    nbytes = ops.attention_workspace_bytes(B, M, P, Hq, Hkv, D)
+    assert nbytes > 0, "case is meant to split"
+    o0, l0 = _run_attention(q, kc, vc, P, causal, scale)
+    qd, kd, vd = q.cuda(), kc.cuda(), vc.cuda()
+    for avail in (nbytes, nbytes // 2 + 256):          # full scratch, and scratch for fewer splits
+        ws = torch.empty(avail, dtype=torch.uint8, device="cuda")
+        ws.fill_(0xff)                                 # contents must not matter (0xff..: NaN as fp32)
+        o1 = torch.zeros(B, M, Hq, D, device="cuda", dtype=dt)
+        l1 = torch.zeros(B, Hq, M, device="cuda")
+        ops.attention(ops.as_bshd(qd, "bshd"), ops.as_bshd(kd, "bhsd"), ops.as_bshd(vd, "bhsd"), ops.as_bshd(o1, "bshd"),
+                      P=P, causal=causal, scale=scale, lse=l1, workspace=ws)
+        torch.cuda.synchronize()
+        assert L.kernel_status() == 0
+        assert not torch.isnan(o1).any()
+        assert (l1 - l0).abs().max().item() <= 1e-4
+        # same softmax, different summation order: within one 16-bit rounding of the unsplit result
+        assert_parity(o1, o0.float().cpu(), "split vs unsplit")
+        r = O.attend(q.float().transpose(1, 2), kc.float(), vc.float(), P=P, causal=causal, scale=scale)
+        assert_parity(o1, r["out"].transpose(1, 2), "split attention output")
+
+
+def test_attention_workspace_is_zero_for_launches_that_fill_the_gpu():
+    assert ops.attention_workspace_bytes(4, 4096, 0, 32, 8, 128) == 0
+    assert ops.attention_workspace_bytes(1, 16, 128, 4, 4, 128) == 0          # two key blocks: nothing to split
+    assert ops.attention_workspace_bytes(1, 16, 1024, 32, 32, 128) > 0
+
+
 def test_attention_single_p_mode_is_looser_but_bounded():
     q, kc, vc = _attn_inputs(1, 256, 0, 2, 2, 128, BF)
     r = O.attend(q.float().transpose(1, 2), kc.float(), vc.float(), P=0, causal=True, scale=128 ** -0.5)

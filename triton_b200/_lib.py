@@ -14,7 +14,7 @@ LIB_NAME = "libtrinity_b200.so"
 # TRINITY_B200_LIB points at another build of the same library (e.g. one compiled with extra -D flags)
 LIB_PATH = Path(os.environ.get("TRINITY_B200_LIB") or (Path(__file__).resolve().parent / LIB_NAME))
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 TRN_BF16, TRN_FP16 = 0, 1
 TRN_VANILLA, TRN_PRENORM, TRN_QKNORM, TRN_KEYFORMER, TRN_ROCO = range(5)
@@ -25,7 +25,8 @@ VARIANTS = {"vanilla": TRN_VANILLA, "prenorm": TRN_PRENORM, "qknorm": TRN_QKNORM
 # every symbol include/trinity_b200.h declares
 EXPORTS = (
     "trinity_abi_version", "trinity_strerror", "trinity_last_cuda_error", "trinity_last_kernel_status",
-    "trinity_rmsnorm", "trinity_qkv_project", "trinity_attention", "trinity_attn_colstats", "trinity_topk",
+    "trinity_rmsnorm", "trinity_qkv_project", "trinity_attention", "trinity_attention_workspace",
+    "trinity_attn_colstats", "trinity_topk",
     "trinity_attn_block_workspace", "trinity_attn_block", "trinity_attn_block_host",
     "trinity_static_scratch_capacity", "trinity_attn_block_static", "trinity_convert",
 )
@@ -61,6 +62,7 @@ class TrnAttnArgs(C.Structure):
         ("dtype", C.c_int), ("causal", C.c_int), ("scale", C.c_float), ("noise_mode", C.c_int), ("tau", C.c_float),
         ("noise", C.c_void_p), ("noise_stride_b", C.c_int64), ("noise_stride_h", C.c_int64),
         ("noise_stride_i", C.c_int64), ("seed", C.c_uint64), ("single_p", C.c_int),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -145,6 +147,8 @@ def load() -> C.CDLL:
         fn.argtypes = [C.POINTER(typ), C.c_void_p]
     lib.trinity_attn_block_workspace.restype = C.c_size_t
     lib.trinity_attn_block_workspace.argtypes = [C.POINTER(TrnBlockArgs)]
+    lib.trinity_attention_workspace.restype = C.c_size_t
+    lib.trinity_attention_workspace.argtypes = [C.POINTER(TrnAttnArgs)]
     lib.trinity_convert.restype = C.c_int
     lib.trinity_convert.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]
     lib.trinity_static_scratch_capacity.restype = C.c_size_t

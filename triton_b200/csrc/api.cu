@@ -125,7 +125,9 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct BlockWorkspace {
-  size_t row_scale_off, lse_off, lse2_off, total;
+  size_t row_scale_off, lse_off, lse2_off, split_off;
+  size_t required;   // the block cannot run with less
+  size_t total;      // required + the optional split-KV area of the attention launches
 };
 
 BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
@@ -139,11 +141,16 @@ BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
   off += align_up(lse * sizeof(float), 256);
   w.lse2_off = off;
   off += align_up(lse * sizeof(float), 256);
-  w.total = off;
+  w.split_off = off;
+  w.required = off;
+  w.total = off + attn_split_workspace(a.B, a.M, a.P, a.Hq, a.Hkv, a.D, kAttnNominalSMs);
   return w;
 }
 
 }  // namespace
+
+size_t block_workspace_required(const TrnBlockArgs& a) { return block_workspace_layout(a).required; }
+
 }  // namespace trn
 
 using namespace trn;
@@ -207,6 +214,11 @@ int trinity_attention(const TrnAttnArgs* a, void* cuda_stream) {
   return launch_attention(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
 }
 
+size_t trinity_attention_workspace(const TrnAttnArgs* a) {
+  if (a == nullptr) return 0;
+  return attn_split_workspace(a->B, a->M, a->P, a->Hq, a->Hkv, a->D, kAttnNominalSMs);
+}
+
 int trinity_attn_colstats(const TrnColStatsArgs* a, void* cuda_stream) {
   if (a == nullptr) return TRN_E_NULL;
   DeviceState* ds = nullptr;
@@ -246,7 +258,7 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
 
   const BlockWorkspace wl = block_workspace_layout(*a);
-  if (a->workspace == nullptr || a->workspace_bytes < wl.total) return TRN_E_WORKSPACE;
+  if (a->workspace == nullptr || a->workspace_bytes < wl.required) return TRN_E_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0) return TRN_E_WORKSPACE;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   float* row_scale = reinterpret_cast<float*>(ws + wl.row_scale_off);
@@ -319,6 +331,9 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
   at.noise_mode = TRN_NOISE_NONE;
   at.tau = 1.0f;
   at.single_p = a->single_p;
+  // what the caller lent beyond the required part serves split-KV (both attention launches, in turn)
+  at.workspace = ws + wl.split_off;
+  at.workspace_bytes = a->workspace_bytes - wl.split_off;
   rc = launch_attention(at, st, *ds);
   if (rc != TRN_OK) return rc;
 

@@ -53,6 +53,12 @@ struct AttnParams {
   float pert_log2;     // MODE 1: log2(e) / tau
   NoiseSrc noise;
   int noise_vec_ok;    // noise tensor base and strides allow 128-bit row loads
+  // split-KV: the key blocks of a CTA's tiles are divided among n_splits CTAs, each of which writes a
+  // normalised fp32 partial output and the base-2 log-sum-exp of its key range; a second kernel merges
+  int n_splits;
+  int ctas_per_split;
+  float* part_o;       // [n_splits, B, Hq, M, D]
+  float* part_lse;     // [n_splits, B, Hq, M]
   int* status;
 };
 
@@ -71,7 +77,8 @@ struct AttnSmem {
 struct TileInfo {
   int h;          // query head
   int q0;         // first query row
-  int n_blocks;   // key blocks this tile visits (0: tile not present)
+  int n_blocks;   // key blocks this CTA visits for the tile
+  bool present;   // the tile exists (it has query rows)
 };
 
 template <typename T, int D, int MODE, bool SPLIT>
@@ -132,8 +139,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   // ---- which two tiles: heavy (late) query blocks first so the causal tail is short
-  const int row_blk = static_cast<int>(blockIdx.x) / p.units;
-  const int unit = static_cast<int>(blockIdx.x) % p.units;
+  const int split = static_cast<int>(blockIdx.x) / p.ctas_per_split;
+  const int cta = static_cast<int>(blockIdx.x) - split * p.ctas_per_split;
+  const int row_blk = cta / p.units;
+  const int unit = cta % p.units;
   int b, kvh;
   TileInfo tile[2];
   if (p.pair_heads) {
@@ -168,6 +177,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tile[t].n_blocks = (kv_end + BKV - 1) / BKV;
     }
   }
+  tile[0].present = tile[0].n_blocks > 0;
+  tile[1].present = tile[1].n_blocks > 0;
+  int j0 = 0;           // first key block of this CTA
+  if (p.n_splits > 1) {
+    const int n_full = max(tile[0].n_blocks, tile[1].n_blocks);
+    j0 = (n_full * split) / p.n_splits;
+    const int j1 = (n_full * (split + 1)) / p.n_splits;
+    tile[0].n_blocks = max(0, min(j1, tile[0].n_blocks) - j0);
+    tile[1].n_blocks = max(0, min(j1, tile[1].n_blocks) - j0);
+  }
   const int n_max = max(tile[0].n_blocks, tile[1].n_blocks);
 
   auto q_s = [&](int t) { return smem_base + SM::kQOff + t * SM::kTileBytes; };
@@ -201,12 +220,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_expect_tx(k_full(st), SM::kTileBytes);
 #pragma unroll
         for (int c = 0; c < SM::kChunks; ++c)
-          tma_load_head_tile(k_s(st) + c * SM::kChunkBytes, &tm_k, k_full(st), p.ki, c * 64, j * BKV, kvh, b);
+          tma_load_head_tile(k_s(st) + c * SM::kChunkBytes, &tm_k, k_full(st), p.ki, c * 64, (j0 + j) * BKV, kvh, b);
         if (MODE == 0) {
           mbar_expect_tx(v_full(st), SM::kTileBytes);
 #pragma unroll
           for (int c = 0; c < SM::kChunks; ++c)
-            tma_load_head_tile(v_s(st) + c * SM::kChunkBytes, &tm_v, v_full(st), p.vi, c * 64, j * BKV, kvh, b);
+            tma_load_head_tile(v_s(st) + c * SM::kChunkBytes, &tm_v, v_full(st), p.vi, c * 64, (j0 + j) * BKV, kvh, b);
         }
       }
       __syncwarp();
@@ -234,11 +253,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       __syncwarp();
     };
-    if (ok) {
+    if (ok && n_max > 0) {
       ok = mbar_wait(k_full(0), 0, ctl, KST_TIMEOUT_MMA);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok) {
+    if (ok && n_max > 0) {
       tc_fence_after();
       for (int t = 0; t < 2; ++t)
         if (tile[t].n_blocks) issue_qk(t, 0);
@@ -326,7 +345,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     : 0u;
 
     for (int j = 0; j < n_blocks; ++j) {
-      const int kv0 = j * BKV;
+      const int kv0 = (j0 + j) * BKV;
       ok = mbar_wait(s_full(t), j & 1, ctl, KST_TIMEOUT_CONSUMER);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -503,6 +522,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive(p_ready(t, 1));
     }
 
+    const bool split_out = p.n_splits > 1;
+    const long long part_row =
+        ((static_cast<long long>(split) * p.B + b) * p.Hq + h) * p.M + q_abs;   // row of the partial results
     if (ok && MODE == 0 && n_blocks > 0) {
       ok = mbar_wait(pv_done(t), (n_blocks - 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
       ok = __all_sync(0xffffffffu, ok);
@@ -511,11 +533,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float inv_l = 1.0f / l_run;
         T* orow = static_cast<T*>(p.o) + static_cast<long long>(b) * p.o_sb + static_cast<long long>(q_abs) * p.o_ss +
                   static_cast<long long>(h) * p.o_sh;
+        float* prow = p.part_o + part_row * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           tmem_ld32(o_tmem + c * 32, r);
           tmem_wait_ld();
-          if (row_valid) {
+          if (row_valid && split_out) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(prow + c * 32 + i) =
+                  make_float4(__uint_as_float(r[i]) * inv_l, __uint_as_float(r[i + 1]) * inv_l,
+                              __uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l);
+          } else if (row_valid) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 v;
@@ -530,8 +559,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_before();
       }
     }
-    if (ok && n_blocks > 0 && row_valid && p.lse != nullptr)
+    if (split_out) {
+      // a CTA whose key range misses this tile contributes weight 0
+      if (ok && tile[t].present && row_valid)
+        p.part_lse[part_row] = (n_blocks > 0) ? m_run + log2f(l_run) : -INFINITY;
+    } else if (ok && n_blocks > 0 && row_valid && p.lse != nullptr) {
       p.lse[(static_cast<long long>(b) * p.Hq + h) * p.M + q_abs] = m_run + log2f(l_run);
+    }
   }
 
   // ------------------------------- teardown -------------------------------
@@ -545,6 +579,66 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemColsAttn);
   }
+}
+
+// Merges the partial results of a split-KV launch: one warp per (b, h, query) row.
+//   w_s = 2^(lse_s - max_s lse_s);  o = sum_s w_s o_s / sum_s w_s;  lse = max + log2(sum_s w_s)
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, T* __restrict__ o,
+                    long long o_sb, long long o_ss, long long o_sh, float* __restrict__ lse_out, int n_splits, int B,
+                    int Hq, int M, const int* __restrict__ status) {
+  if (*reinterpret_cast<const volatile int*>(status) != 0) return;
+  constexpr int VPL = D / 32;
+  const long long rows = static_cast<long long>(B) * Hq * M;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_lse[s * rows + row]);
+  float tot = 0.f;
+  float acc[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ls = part_lse[s * rows + row];
+    if (ls == -INFINITY) continue;             // this split saw no key of the row: its o was not written
+    const float w = ex2_approx(ls - m);
+    tot += w;
+    if (part_o != nullptr) {
+      const float* src = part_o + (s * rows + row) * D + lane * VPL;
+      if constexpr (VPL == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src);
+        acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
+        acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+      } else {
+        const float2 v = *reinterpret_cast<const float2*>(src);
+        acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
+      }
+    }
+  }
+  const int q = static_cast<int>(row % M);
+  const int h = static_cast<int>((row / M) % Hq);
+  const int b = static_cast<int>(row / (static_cast<long long>(M) * Hq));
+  if (part_o != nullptr) {
+    const float inv = 1.0f / tot;
+    T* dst = o + b * o_sb + q * o_ss + h * o_sh + lane * VPL;
+    if constexpr (VPL == 4) {
+      uint2 v;
+      v.x = Io<T>::pack2(acc[0] * inv, acc[1] * inv);
+      v.y = Io<T>::pack2(acc[2] * inv, acc[3] * inv);
+      *reinterpret_cast<uint2*>(dst) = v;
+    } else {
+      *reinterpret_cast<uint32_t*>(dst) = Io<T>::pack2(acc[0] * inv, acc[1] * inv);
+    }
+  }
+  if (lse_out != nullptr && lane == 0) lse_out[row] = m + log2f(tot);
+}
+
+size_t split_bytes(int n_splits, long long rows, int D, bool with_o) {
+  const size_t o_b = with_o ? (static_cast<size_t>(n_splits) * rows * D * sizeof(float) + 255) / 256 * 256 : 0;
+  const size_t l_b = (static_cast<size_t>(n_splits) * rows * sizeof(float) + 255) / 256 * 256;
+  return o_b + l_b;
 }
 
 template <typename T, int D, int MODE, bool SPLIT>
@@ -595,10 +689,31 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   auto kern = attn_fwd_kernel<T, D, MODE, SPLIT>;
   rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
   if (rc != TRN_OK) return rc;
-  const long long grid = rows_of_ctas * p.units;
-  if (grid > 0x7fffffffLL) return TRN_E_SHAPE;
-  kern<<<static_cast<int>(grid), kAttnThreads, SM::kTotal, st>>>(tm_q, tm_k, tm_v, p);
+  const long long ctas = rows_of_ctas * p.units;
+  if (ctas > 0x7fffffffLL) return TRN_E_SHAPE;
+  // split-KV when the launch would leave most SMs idle and the caller lent scratch for the partials
+  const long long rows = static_cast<long long>(a.B) * a.Hq * a.M;
+  int n_splits = attn_split_count(static_cast<int>(ctas), L, ds.sm_count);
+  if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0) n_splits = 1;
+  while (n_splits > 1 && split_bytes(n_splits, rows, D, MODE == 0) > a.workspace_bytes) --n_splits;
+  p.n_splits = n_splits;
+  p.ctas_per_split = static_cast<int>(ctas);
+  if (n_splits > 1) {
+    uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+    const size_t l_b = split_bytes(n_splits, rows, D, false);
+    p.part_lse = reinterpret_cast<float*>(ws);
+    p.part_o = (MODE == 0) ? reinterpret_cast<float*>(ws + l_b) : nullptr;
+  }
+  kern<<<static_cast<int>(ctas * n_splits), kAttnThreads, SM::kTotal, st>>>(tm_q, tm_k, tm_v, p);
   TRN_CUDA_TRY(cudaGetLastError());
+  if (n_splits > 1) {
+    const int warps_per_cta = 8;
+    const long long cgrid = (rows + warps_per_cta - 1) / warps_per_cta;
+    attn_combine_kernel<T, D><<<static_cast<int>(cgrid), warps_per_cta * 32, 0, st>>>(
+        p.part_o, p.part_lse, static_cast<T*>(a.o.ptr), a.o.stride_b, a.o.stride_s, a.o.stride_h, a.lse, n_splits,
+        a.B, a.Hq, a.M, ds.status);
+    TRN_CUDA_TRY(cudaGetLastError());
+  }
   return TRN_OK;
 }
 
@@ -623,6 +738,24 @@ bool ht_ok(const TrnHeadTensor& t) {
 
 }  // namespace
 
+
+int attn_split_count(int ctas, int L, int sm_count) {
+  const int n_blocks = (L + BKV - 1) / BKV;
+  if (ctas <= 0) return 1;
+  const int want = min(min(sm_count / ctas, n_blocks / 2), kAttnMaxSplits);
+  return want >= 2 ? want : 1;
+}
+
+size_t attn_split_workspace(int B, int M, int P, int Hq, int Hkv, int D, int sm_count) {
+  if (B <= 0 || M <= 0 || P < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || (D != 64 && D != 128)) return 0;
+  const int group = Hq / Hkv;
+  const long long n_qb = (M + BQ - 1) / BQ;
+  const long long ctas = group >= 2 ? n_qb * B * Hkv * ((group + 1) / 2) : ((n_qb + 1) / 2) * B * Hq;
+  if (ctas > sm_count) return 0;
+  const int n = attn_split_count(static_cast<int>(ctas), P + M, sm_count);
+  if (n <= 1) return 0;
+  return split_bytes(n, static_cast<long long>(B) * Hq * M, D, true);
+}
 
 int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (a.B <= 0 || a.M <= 0 || a.P < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.Hq % a.Hkv != 0) return TRN_E_SHAPE;

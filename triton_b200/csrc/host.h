@@ -48,6 +48,14 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int launch_rmsnorm(const TrnRmsArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_qkv_project(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
+// split-KV policy of the attention kernel: how many CTAs share one tile pair's key range (1: no split),
+// and the scratch a launch of that shape wants for the partial results (0: it would not split)
+constexpr int kAttnMaxSplits = 8;
+constexpr int kAttnNominalSMs = 148;     // sizing only: the launch itself uses the device's SM count
+int attn_split_count(int ctas, int L, int sm_count);
+size_t attn_split_workspace(int B, int M, int P, int Hq, int Hkv, int D, int sm_count);
+// smallest workspace trinity_attn_block accepts (its optional split-KV area excluded)
+size_t block_workspace_required(const TrnBlockArgs& a);
 int launch_colstats(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_topk(const TrnTopkArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_convert(const void* src, void* dst, long long n, int dtype16, int to_fp32, cudaStream_t st,

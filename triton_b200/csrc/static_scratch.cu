@@ -49,8 +49,9 @@ extern "C" size_t trinity_static_scratch_capacity(void) { return kStaticScratchB
 
 extern "C" int trinity_attn_block_static(const TrnBlockArgs* a, void* cuda_stream) {
   if (a == nullptr) return TRN_E_NULL;
-  const size_t need = trinity_attn_block_workspace(a);
-  if (need == 0) return TRN_E_SHAPE;
+  if (trinity_attn_block_workspace(a) == 0) return TRN_E_SHAPE;
+  // the optional split-KV area is used as far as the array reaches; only the required part must fit
+  const size_t need = block_workspace_required(*a);
   if (need > kStaticScratchBytes) return TRN_E_STATIC_SCRATCH;   // too large for the built-in scratch
   void* scratch = nullptr;
   int rc = static_scratch_address(&scratch);

@@ -127,9 +127,11 @@ def _noise_fields(noise: Optional[torch.Tensor]):
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o: Optional[torch.Tensor], *,
               P: int, causal: bool, scale: float, lse: Optional[torch.Tensor] = None,
               noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
-              seed: int = 0, single_p: bool = False) -> None:
-    """o = softmax(scale * q k^T [causal]) v over keys [0, P+M).  All tensors are (b, s, h, d) views."""
-    _need_cuda(q, k_cache, v_cache, o, lse, noise)
+              seed: int = 0, single_p: bool = False, workspace: Optional[torch.Tensor] = None) -> None:
+    """o = softmax(scale * q k^T [causal]) v over keys [0, P+M).  All tensors are (b, s, h, d) views.
+    ``workspace`` (a uint8 CUDA tensor of attention_workspace_bytes(...) bytes) lets small launches
+    split the key range over more CTAs."""
+    _need_cuda(q, k_cache, v_cache, o, lse, noise, workspace)
     B, M, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     if k_cache.shape[1] < P + M or v_cache.shape[1] < P + M:
@@ -137,8 +139,16 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o: 
     nptr, nb, nh, ni = _noise_fields(noise)
     a = L.TrnAttnArgs(_head_tensor(q), _head_tensor(k_cache), _head_tensor(v_cache), _head_tensor(o), _ptr(lse),
                       B, M, P, Hq, Hkv, D, _dtype_code(q), int(causal), float(scale), noise_mode, float(tau),
-                      nptr, nb, nh, ni, seed, int(single_p))
+                      nptr, nb, nh, ni, seed, int(single_p), _ptr(workspace),
+                      0 if workspace is None else workspace.numel() * workspace.element_size())
     L.check(L.load().trinity_attention(C.byref(a), _stream()))
+
+
+def attention_workspace_bytes(B: int, M: int, P: int, Hq: int, Hkv: int, D: int) -> int:
+    """Scratch with which trinity_attention would split the key range for this shape (0: it would not)."""
+    a = L.TrnAttnArgs()
+    a.B, a.M, a.P, a.Hq, a.Hkv, a.D = B, M, P, Hq, Hkv, D
+    return int(L.load().trinity_attention_workspace(C.byref(a)))
 
 
 def attn_colstats(q: torch.Tensor, k_cache: torch.Tensor, lse: torch.Tensor, sum_p: torch.Tensor,
