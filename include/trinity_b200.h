@@ -258,6 +258,10 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream);
  * `cuda_stream`, copies o back to o_host (and the statistics when the pointers are given) and
  * synchronises the stream.  x_dev_staging / o (device) are caller buffers as above.  Weights and
  * caches stay device-resident (they are the model's state, not a per-call input).
+ * With B >= 2, batch-major contiguous x / o and at least 4 MB to move, the call works through the batch in
+ * up to 8 groups: group c+1 is copied in and group c-1 copied out (two internal copy streams, created on
+ * the first such call on a device) while group c computes on `cuda_stream`; the outputs are bit-identical
+ * to the one-pass call.  Pinned host buffers are needed for the copies to overlap.
  * ---------------------------------------------------------------------------------------------- */
 typedef struct {
   TrnBlockArgs dev;        /* dev.x must point at the device staging buffer for x */

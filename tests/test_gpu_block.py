@@ -230,3 +230,52 @@ def test_fp32_vanilla_configuration():
     assert_parity(T["O2"].view(512, 32, 128), r["out_bmhd"][0], "fp32 vanilla out", rel_floor=REL_FLOOR_FP32,
                   rel_tol=REL_TOL_E2E)
     assert_parity(T["K_cache"], r["k_all"][0], "fp32 vanilla k", rel_floor=REL_FLOOR_FP32, rel_tol=REL_TOL_E2E)
+
+
+@pytest.mark.parametrize("variant,B,stats", (("prenorm", 4, False), ("roco", 3, True), ("keyformer", 9, True)))
+def test_host_activation_path_pipelines_batch_items_with_identical_results(variant, B, stats):
+    """trinity_attn_block_host copies batch items in and out while others compute; every output element
+    must equal the one-pass device result bit for bit (odd batch counts: uneven last group)."""
+    M, P, N, Hq, Hkv, D = 512, 64, 1024, 8, 2, 128        # x and o: 1 MB per batch item each
+    L_ = P + M
+    torch.manual_seed(31)
+    dt = BF
+    x = torch.randn(B * M, N).to(dt)
+    wq, wk, wv = ((torch.randn(N, h * D) / N ** 0.5).to(dt).cuda() for h in (Hq, Hkv, Hkv))
+    kc0, vc0 = torch.randn(B, Hkv, L_, D).to(dt), torch.randn(B, Hkv, L_, D).to(dt)
+    noise = torch.randn(B, Hq, M, L_).to(dt).cuda() if variant == "keyformer" else None
+    gamma = (1 + 0.1 * torch.randn(N)).to(dt).cuda() if variant == "prenorm" else None
+
+    def make():
+        kc, vc = kc0.clone().cuda(), vc0.clone().cuda()
+        q = torch.zeros(B, M, Hq, D, dtype=dt, device="cuda")
+        o = torch.zeros(B, M, Hq, D, dtype=dt, device="cuda")
+        sp = torch.zeros(B, Hq, L_, device="cuda") if stats else None
+        sp2 = torch.zeros(B, Hq, L_, device="cuda") if variant == "roco" else None
+        xd = torch.zeros(B * M, N, dtype=dt, device="cuda")
+        plan = ops.BlockPlan(variant, B=B, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, q=q, k_cache=ops.as_bshd(kc, "bhsd"),
+                             v_cache=ops.as_bshd(vc, "bhsd"), o=o, x=xd, wq=wq, wk=wk, wv=wv, causal=True,
+                             scale=D ** -0.5, pre_eps=1e-5, pre_gamma=gamma,
+                             noise_mode=L.TRN_NOISE_TENSOR if variant == "keyformer" else L.TRN_NOISE_NONE, tau=1.5,
+                             noise=noise, sum_p=sp, sum_p2=sp2)
+        return plan, xd, o, kc, vc, sp, sp2
+
+    plan, xd, o_ref, kc_ref, vc_ref, sp_ref, sp2_ref = make()
+    xd.copy_(x)
+    plan.run()
+    torch.cuda.synchronize()
+
+    plan2, xd2, o2, kc2, vc2, sp_d, sp2_d = make()
+    xh = x.clone().pin_memory()
+    oh = torch.zeros(B, M, Hq, D, dtype=dt).pin_memory()
+    sph = torch.zeros(B, Hq, L_).pin_memory() if stats else None
+    sp2h = torch.zeros(B, Hq, L_).pin_memory() if variant == "roco" else None
+    for _ in range(2):                               # the second call reuses the streams and events
+        plan2.run_host(xh, oh, sph, sp2h)
+    assert L.kernel_status() == 0
+    assert torch.equal(oh, o_ref.cpu())
+    assert torch.equal(kc2, kc_ref) and torch.equal(vc2, vc_ref)
+    if stats:
+        assert torch.equal(sph, sp_ref.cpu())
+    if sp2h is not None:
+        assert torch.equal(sp2h, sp2_ref.cpu())

@@ -149,6 +149,52 @@ BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
 
 }  // namespace
 
+// ---- host-activation pipeline (trinity_attn_block_host): two copy streams and a few events per device,
+// created on the first call that pipelines
+constexpr int kHostMaxChunks = 8;
+struct HostPipe {
+  bool ready = false;
+  cudaStream_t in = nullptr, out = nullptr;
+  cudaEvent_t ev[2 + 2 * kHostMaxChunks] = {};
+};
+HostPipe g_host_pipe[kMaxDevices];
+std::mutex g_host_pipe_mu;
+
+int get_host_pipe(HostPipe** out) {
+  int dev = -1;
+  TRN_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return TRN_E_DEVICE;
+  std::lock_guard<std::mutex> lock(g_host_pipe_mu);
+  HostPipe& hp = g_host_pipe[dev];
+  if (!hp.ready) {
+    TRN_CUDA_TRY(cudaStreamCreateWithFlags(&hp.in, cudaStreamNonBlocking));
+    TRN_CUDA_TRY(cudaStreamCreateWithFlags(&hp.out, cudaStreamNonBlocking));
+    for (auto& e : hp.ev) TRN_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    hp.ready = true;
+  }
+  *out = &hp;
+  return TRN_OK;
+}
+
+// How many batch groups the host path pipelines (1: one pass).  It pipelines when the batch items are
+// separate contiguous slabs on both sides and the copies are large enough to be worth overlapping.
+int host_chunk_count(const TrnBlockHostArgs& a) {
+  const TrnBlockArgs& d = a.dev;
+  if (d.B < 2 || d.M <= 0 || d.N <= 0) return 1;
+  if (a.x_bytes + a.o_bytes < (4u << 20)) return 1;
+  if (a.x_bytes != static_cast<size_t>(d.B) * d.M * d.N * 2) return 1;
+  // o: batch-major slabs that tile o_bytes exactly
+  if (d.o.stride_b <= 0 || static_cast<size_t>(d.o.stride_b) * 2 * d.B != a.o_bytes) return 1;
+  if (d.o.stride_b < d.o.stride_s * d.M || d.o.stride_b < d.o.stride_h * d.Hq) return 1;
+  if (a.stats_bytes % d.B != 0) return 1;
+  if ((d.sum_p != nullptr || d.sum_p2 != nullptr) &&
+      a.stats_bytes != 0 && a.stats_bytes != static_cast<size_t>(d.B) * d.Hq * (d.P + d.M) * (d.stats_fp32 ? 4 : 2))
+    return 1;
+  // generated KeyFormer noise is keyed by the batch index inside a launch: keep such a block in one pass
+  if (d.variant == TRN_KEYFORMER && d.noise_mode == TRN_NOISE_GUMBEL) return 1;
+  return d.B < kHostMaxChunks ? d.B : kHostMaxChunks;
+}
+
 size_t block_workspace_required(const TrnBlockArgs& a) { return block_workspace_layout(a).required; }
 
 }  // namespace trn
@@ -385,6 +431,80 @@ int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream) {
   if (a == nullptr || a->x_host == nullptr || a->o_host == nullptr) return TRN_E_NULL;
   if (a->dev.x == nullptr || a->dev.o.ptr == nullptr) return TRN_E_NULL;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  const TrnBlockArgs& d = a->dev;
+  HostPipe* hp = nullptr;
+  const int chunks = host_chunk_count(*a);
+  if (chunks > 1 && get_host_pipe(&hp) == TRN_OK) {
+    // Batch items are independent: copy item group c+1 in while group c computes and group c-1 copies out
+    // (PCIe is full duplex; the copies run on two streams of the library, ordered against the caller's
+    // stream by events).  Per-element results are the same as in one pass: each output element is computed
+    // by the same instructions in the same order whichever rows share its launch.
+    const int per = (d.B + chunks - 1) / chunks;
+    DeviceState* ds = nullptr;
+    int rcd = get_device_state(&ds);
+    if (rcd != TRN_OK) return rcd;
+    // every group uses the split-KV count of the uncut problem
+    struct SplitGuard {
+      explicit SplitGuard(int n) { tls_attn_split_override = n; }
+      ~SplitGuard() { tls_attn_split_override = 0; }
+    } guard(attn_planned_splits(d.B, d.M, d.P, d.Hq, d.Hkv, d.D, ds->sm_count));
+    const size_t esz = 2;
+    const size_t stat_esz = d.stats_fp32 ? 4 : 2;
+    const size_t x_item = a->x_bytes / d.B, o_item = a->o_bytes / d.B;
+    const size_t stats_item = (a->stats_bytes != 0) ? a->stats_bytes / d.B : 0;
+    TRN_CUDA_TRY(cudaEventRecord(hp->ev[0], st));
+    TRN_CUDA_TRY(cudaStreamWaitEvent(hp->in, hp->ev[0], 0));
+    TRN_CUDA_TRY(cudaStreamWaitEvent(hp->out, hp->ev[0], 0));
+    int n = 0;
+    for (int b0 = 0; b0 < d.B; b0 += per, ++n) {
+      const int nb = (d.B - b0 < per) ? d.B - b0 : per;
+      TRN_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(const_cast<void*>(d.x)) + b0 * x_item,
+                                   static_cast<const uint8_t*>(a->x_host) + b0 * x_item, nb * x_item,
+                                   cudaMemcpyHostToDevice, hp->in));
+      TRN_CUDA_TRY(cudaEventRecord(hp->ev[1 + 2 * n], hp->in));
+    }
+    n = 0;
+    for (int b0 = 0; b0 < d.B; b0 += per, ++n) {
+      const int nb = (d.B - b0 < per) ? d.B - b0 : per;
+      TrnBlockArgs c = d;
+      c.B = nb;
+      auto adv = [&](const void* ptr, size_t bytes_per_item) -> void* {
+        return ptr == nullptr ? nullptr : static_cast<uint8_t*>(const_cast<void*>(ptr)) + b0 * bytes_per_item;
+      };
+      c.x = adv(d.x, x_item);
+      c.x_norm = adv(d.x_norm, x_item);
+      c.q.ptr = adv(d.q.ptr, d.q.stride_b * esz);
+      c.k_cache.ptr = adv(d.k_cache.ptr, d.k_cache.stride_b * esz);
+      c.v_cache.ptr = adv(d.v_cache.ptr, d.v_cache.stride_b * esz);
+      c.o.ptr = adv(d.o.ptr, d.o.stride_b * esz);
+      c.noise = adv(d.noise, d.noise_stride_b * esz);
+      const size_t stats_dev_item = static_cast<size_t>(d.Hq) * (d.P + d.M) * stat_esz;
+      c.sum_p = adv(d.sum_p, stats_dev_item);
+      c.sum_p2 = adv(d.sum_p2, stats_dev_item);
+      TRN_CUDA_TRY(cudaStreamWaitEvent(st, hp->ev[1 + 2 * n], 0));
+      int rc = trinity_attn_block(&c, cuda_stream);
+      if (rc != TRN_OK) {
+        cudaStreamSynchronize(hp->in);      // leave no copy of this call in flight
+        cudaStreamSynchronize(st);
+        return rc;
+      }
+      TRN_CUDA_TRY(cudaEventRecord(hp->ev[2 + 2 * n], st));
+      TRN_CUDA_TRY(cudaStreamWaitEvent(hp->out, hp->ev[2 + 2 * n], 0));
+      TRN_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(a->o_host) + b0 * o_item,
+                                   static_cast<const uint8_t*>(d.o.ptr) + b0 * o_item, nb * o_item,
+                                   cudaMemcpyDeviceToHost, hp->out));
+      if (a->sum_p_host != nullptr && d.sum_p != nullptr)
+        TRN_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(a->sum_p_host) + b0 * stats_item, c.sum_p, nb * stats_item,
+                                     cudaMemcpyDeviceToHost, hp->out));
+      if (a->sum_p2_host != nullptr && d.sum_p2 != nullptr)
+        TRN_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(a->sum_p2_host) + b0 * stats_item, c.sum_p2, nb * stats_item,
+                                     cudaMemcpyDeviceToHost, hp->out));
+    }
+    TRN_CUDA_TRY(cudaEventRecord(hp->ev[1 + 2 * kHostMaxChunks], hp->out));
+    TRN_CUDA_TRY(cudaStreamWaitEvent(st, hp->ev[1 + 2 * kHostMaxChunks], 0));
+    TRN_CUDA_TRY(cudaStreamSynchronize(st));
+    return TRN_OK;
+  }
   TRN_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(a->dev.x), a->x_host, a->x_bytes, cudaMemcpyHostToDevice, st));
   int rc = trinity_attn_block(&a->dev, cuda_stream);
   if (rc != TRN_OK) return rc;

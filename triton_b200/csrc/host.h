@@ -54,6 +54,12 @@ constexpr int kAttnMaxSplits = 8;
 constexpr int kAttnNominalSMs = 148;     // sizing only: the launch itself uses the device's SM count
 int attn_split_count(int ctas, int L, int sm_count);
 size_t attn_split_workspace(int B, int M, int P, int Hq, int Hkv, int D, int sm_count);
+// the split count a launch of this shape picks when its workspace is large enough
+int attn_planned_splits(int B, int M, int P, int Hq, int Hkv, int D, int sm_count);
+// > 0: attention launches made by this thread use exactly this many splits (workspace permitting) instead
+// of their own choice; set by callers that cut one problem into several launches and want each output
+// element computed as the uncut launch would
+extern thread_local int tls_attn_split_override;
 // smallest workspace trinity_attn_block accepts (its optional split-KV area excluded)
 size_t block_workspace_required(const TrnBlockArgs& a);
 int launch_colstats(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds);

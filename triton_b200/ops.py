@@ -240,6 +240,23 @@ class BlockPlan:
     def run(self) -> None:
         L.check(self._lib.trinity_attn_block(C.byref(self.args), _stream()))
 
+    def run_host(self, x_host: torch.Tensor, o_host: torch.Tensor, sum_p_host: Optional[torch.Tensor] = None,
+                 sum_p2_host: Optional[torch.Tensor] = None) -> None:
+        """The block with HOST activations (trinity_attn_block_host): x_host -> the plan's device x, the block,
+        o (and the statistics) -> host.  Pinned buffers let the copies of different batch items overlap
+        with the kernels.  Returns after the stream has drained."""
+        for t in (x_host, o_host, sum_p_host, sum_p2_host):
+            if t is not None and (t.is_cuda or not t.is_contiguous()):
+                raise ValueError("run_host needs contiguous host tensors")
+        h = L.TrnBlockHostArgs()
+        C.memmove(C.byref(h.dev), C.byref(self.args), C.sizeof(L.TrnBlockArgs))
+        h.x_host, h.o_host = x_host.data_ptr(), o_host.data_ptr()
+        h.x_bytes = x_host.numel() * x_host.element_size()
+        h.o_bytes = o_host.numel() * o_host.element_size()
+        h.sum_p_host, h.sum_p2_host = _ptr(sum_p_host), _ptr(sum_p2_host)
+        h.stats_bytes = 0 if sum_p_host is None else sum_p_host.numel() * sum_p_host.element_size()
+        L.check(self._lib.trinity_attn_block_host(C.byref(h), _stream()))
+
 
 def convert(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
     """fp32 -> bf16/fp16 (rounding) or bf16/fp16 -> fp32 (widening) of contiguous tensors of equal numel."""
