@@ -301,6 +301,17 @@ int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream);
 size_t trinity_static_scratch_capacity(void);
 int trinity_attn_block_static(const TrnBlockArgs* a, void* cuda_stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Diagnostic, no reference counterpart: SM clocks per tcgen05.mma (M = 128, K = 16, kind::f16, bf16
+ * operands, fp32 accumulation) when one thread issues n_mma of them back to back on every SM, with
+ * operands resident on chip.  SS: A and B from shared memory; TS: A from tensor memory (the P v product of
+ * the attention kernel).  with_tmem_traffic != 0 adds eight warps that stream tcgen05.ld / st over other
+ * tensor-memory columns, as softmax warps do.  Synchronous; allocates 8 bytes for the result.  These are
+ * the per-instruction ceilings the GEMM (SS N256) and attention (SS N128, TS N128 / N64) kernels run under.
+ * ---------------------------------------------------------------------------------------------- */
+enum { TRN_MMA_SS_N64 = 0, TRN_MMA_SS_N128 = 1, TRN_MMA_SS_N256 = 2, TRN_MMA_TS_N128 = 3, TRN_MMA_TS_N64 = 4 };
+int trinity_probe_mma_rate(int shape, int with_tmem_traffic, int n_mma, double* clocks_per_mma);
+
 #ifdef __cplusplus
 }
 #endif

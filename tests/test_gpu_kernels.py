@@ -289,3 +289,14 @@ def test_topk_edge_cases():
         ops.topk_keys(torch.randn(2, 9000, device="cuda"), 10)
     with pytest.raises(L.TrinityError, match="shape"):
         ops.topk_keys(odd, 2000)
+
+
+def test_mma_rate_probe_reports_plausible_clocks():
+    from triton_b200 import mma_rate
+    rows = {r["shape"]: r for r in mma_rate.measure(n_mma=1024)}
+    assert L.kernel_status() == 0
+    for r in rows.values():
+        assert 30.0 < r["clk_per_mma"] < 1000.0
+    # twice the columns never cost less than half as much again per instruction
+    assert rows["SS N256"]["clk_per_mma"] >= rows["SS N128"]["clk_per_mma"]
+    assert rows["SS N256"]["mac_per_clk_per_sm"] <= 4096 * 1.05     # the nominal dense bf16 rate per SM

@@ -28,7 +28,7 @@ EXPORTS = (
     "trinity_rmsnorm", "trinity_qkv_project", "trinity_attention", "trinity_attention_workspace",
     "trinity_attn_colstats", "trinity_topk",
     "trinity_attn_block_workspace", "trinity_attn_block", "trinity_attn_block_host",
-    "trinity_static_scratch_capacity", "trinity_attn_block_static", "trinity_convert",
+    "trinity_static_scratch_capacity", "trinity_attn_block_static", "trinity_convert", "trinity_probe_mma_rate",
 )
 
 
@@ -149,6 +149,8 @@ def load() -> C.CDLL:
     lib.trinity_attn_block_workspace.argtypes = [C.POINTER(TrnBlockArgs)]
     lib.trinity_attention_workspace.restype = C.c_size_t
     lib.trinity_attention_workspace.argtypes = [C.POINTER(TrnAttnArgs)]
+    lib.trinity_probe_mma_rate.restype = C.c_int
+    lib.trinity_probe_mma_rate.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
     lib.trinity_convert.restype = C.c_int
     lib.trinity_convert.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]
     lib.trinity_static_scratch_capacity.restype = C.c_size_t
