@@ -105,16 +105,24 @@ __device__ __forceinline__ float lg2_approx(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// g = -ln(-ln u), u = (k + 0.5) / 2^23 with k the top 23 bits.  Two MUFU log2 plus a short series for
-// -ln u when u is within 2^-6 of 1 (where log2's absolute error would dominate): relative error of the
-// inner logarithm <= ~1e-5, absolute error of g of the same order.
+// g = -ln(-ln u), u = (k + 0.5) / 2^23 with k the top 23 bits.  Two MUFU log2; when u is within 2^-10 of 1
+// (where log2's absolute error, ~2^-22, would dominate) -ln u comes from the series v + v^2/2 of v = 1 - u
+// instead (truncation < 3e-7 relative).  Relative error of the inner logarithm <= ~2e-4, absolute error of
+// g of the same order.
+constexpr float kGumbelSeriesBelow = 0.0009765625f;   // 2^-10
+// u and 1 - u are built from the bits without an integer-to-float conversion (those share the MUFU pipe with
+// the logarithms): 0x3f800000 | k is the float 1 + k 2^-23, and subtracting 1 - 2^-24 leaves (k + 0.5) 2^-23
+// exactly; 0x7fffff - k = k ^ 0x7fffff gives 1 - u the same way.
+__device__ __forceinline__ float unit_from_23bits(uint32_t k) {
+  return __uint_as_float(0x3f800000u | k) - 0.999999940395355224609375f;
+}
 __device__ __forceinline__ float gumbel_from_bits(uint32_t bits) {
   const uint32_t k = bits >> 9;
-  const float u = (static_cast<float>(k) + 0.5f) * 1.1920928955078125e-07f;                    // 2^-23
-  const float v = (static_cast<float>(0x7fffffu - k) + 0.5f) * 1.1920928955078125e-07f;        // 1 - u, exact
+  const float u = unit_from_23bits(k);
+  const float v = unit_from_23bits(k ^ 0x7fffffu);                                             // 1 - u, exact
   const float w_log = -0.6931471805599453f * lg2_approx(u);
-  const float w_ser = v * fmaf(v, fmaf(v, fmaf(v, 0.25f, 0.3333333333f), 0.5f), 1.0f);         // v + v^2/2 + v^3/3 + v^4/4
-  const float w = (v < 0.015625f) ? w_ser : w_log;
+  const float w_ser = fmaf(0.5f * v, v, v);                                                     // v + v^2/2
+  const float w = (v < kGumbelSeriesBelow) ? w_ser : w_log;
   return -0.6931471805599453f * lg2_approx(w);
 }
 
@@ -122,11 +130,11 @@ __device__ __forceinline__ float gumbel_from_bits(uint32_t bits) {
 // log2 domain fold the constant into their own scale
 __device__ __forceinline__ float gumbel_log2e_from_bits(uint32_t bits) {
   const uint32_t k = bits >> 9;
-  const float u = fmaf(static_cast<float>(k), 1.1920928955078125e-07f, 5.9604644775390625e-08f);
-  const float v = fmaf(static_cast<float>(0x7fffffu - k), 1.1920928955078125e-07f, 5.9604644775390625e-08f);
+  const float u = unit_from_23bits(k);
+  const float v = unit_from_23bits(k ^ 0x7fffffu);
   const float w_log = -0.6931471805599453f * lg2_approx(u);
-  const float w_ser = v * fmaf(v, fmaf(v, fmaf(v, 0.25f, 0.3333333333f), 0.5f), 1.0f);
-  return lg2_approx((v < 0.015625f) ? w_ser : w_log);
+  const float w_ser = fmaf(0.5f * v, v, v);
+  return lg2_approx((v < kGumbelSeriesBelow) ? w_ser : w_log);
 }
 
 struct NoiseSrc {
