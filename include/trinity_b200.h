@@ -225,7 +225,9 @@ typedef struct {
   /* PreNorm */
   float pre_eps;
   const void* pre_gamma; /* [N] or NULL; when given, x_norm scratch [B*M, N] must be supplied */
-  void* x_norm;          /* [B*M, N] scratch, required only with pre_gamma */
+  void* x_norm;          /* [B*M, N]: required with pre_gamma.  Given without gamma it selects the two-step
+                            schedule too: X_norm is written here (rounded to the io type) and projected,
+                            instead of the row scale being folded into the projection's epilogue      */
   /* QKNorm */
   float qk_eps;
   const void* gamma_q;

@@ -35,7 +35,7 @@ def test_parser_builds_reference_tree(name):
 @pytest.mark.parametrize("name", PROGRAMS)
 def test_recogniser_matches_reference_metadata(name):
     prog = recognise(IRParser().parse(read(name)), SHAPE_DICT)
-    assert prog.variant == name
+    assert prog.variant == name.split("_")[0]          # prenorm_fused is a second PreNorm candidate
     assert prog.tensor_params == META[name]["tensor_params"]
     assert prog.block_params == META[name]["block_params"]
     assert prog.n_kernels == META[name]["n_kernels"]
@@ -103,3 +103,22 @@ def test_ir_file_format(tmp_path):
     assert tree(IRParser().parse(got[0][1])) == META["vanilla"]["ast"]
     assert parse_ir_file(os.path.join(IR_DIR, "roco.txt"))[0][0] == 0
     assert resolve_dim("P+M", MODEL_CONFIGS["llama"]) == 1040 and resolve_dim(5, {}) == 5
+
+
+def test_schedule_follows_the_candidates_fusion_structure():
+    """The launch-plan choices the recogniser derives from a candidate's loop / fusion structure."""
+    from triton_b200.ir import IRParser
+    from triton_b200.recognise import recognise
+    ir_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "triton_b200", "ir_programs")
+    progs = {n: recognise(IRParser().parse(open(os.path.join(ir_dir, n + ".txt")).read()))
+             for n in ("vanilla", "prenorm", "prenorm_fused", "keyformer", "roco", "rmsnorm")}
+    assert progs["prenorm"].variant == progs["prenorm_fused"].variant == "prenorm"
+    assert progs["prenorm"].schedule["x_norm_in_memory"] is True          # a kernel of its own stores X_norm
+    assert progs["prenorm_fused"].schedule["x_norm_in_memory"] is False   # normalised inside the projection loop
+    assert progs["prenorm"].schedule["kernels"] == 4 and progs["prenorm_fused"].schedule["kernels"] == 3
+    assert progs["vanilla"].schedule == {"kernels": 2, "in_memory": [], "x_norm_in_memory": False,
+                                         "scores_in_memory": []}
+    # candidates that keep a [H, M, P+M] score tensor in memory: accepted, the kernels never materialise it
+    assert progs["keyformer"].schedule["scores_in_memory"] == ["C_exp_perturb"]
+    assert progs["roco"].schedule["scores_in_memory"] == ["C_exp"]
+    assert progs["rmsnorm"].schedule["in_memory"] == ["X2"]

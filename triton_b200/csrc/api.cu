@@ -329,9 +329,10 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
       r.y_row_stride = a->N;
       r.eps = a->pre_eps;
       r.dtype = a->dtype;
-      if (a->pre_gamma != nullptr) {
+      if (a->pre_gamma != nullptr || a->x_norm != nullptr) {
         // gamma scales the hidden (contraction) axis, so it cannot move to the GEMM epilogue:
-        // materialise x_norm once, then project it.
+        // materialise x_norm once, then project it.  A caller that passes x_norm without gamma asks for
+        // the same two-step schedule (its program stores X_norm as a tensor of its own).
         if (a->x_norm == nullptr) return TRN_E_NULL;
         r.y = a->x_norm;
         r.gamma = a->pre_gamma;

@@ -197,8 +197,8 @@ class BlockPlan:
                  gamma_k: Optional[torch.Tensor] = None,
                  noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
                  seed: int = 0, sum_p: Optional[torch.Tensor] = None, sum_p2: Optional[torch.Tensor] = None,
-                 single_p: bool = False):
-        _need_cuda(q, k_cache, v_cache, o, x, wq, wk, wv, pre_gamma, gamma_q, gamma_k, noise, sum_p, sum_p2)
+                 single_p: bool = False, x_norm: Optional[torch.Tensor] = None):
+        _need_cuda(q, k_cache, v_cache, o, x, wq, wk, wv, pre_gamma, gamma_q, gamma_k, noise, sum_p, sum_p2, x_norm)
         self.variant = variant
         skip = x is None
         N = 0 if skip else x.shape[-1]
@@ -216,7 +216,13 @@ class BlockPlan:
             a.x, a.wq, a.wk, a.wv = x.data_ptr(), wq.data_ptr(), wk.data_ptr(), wv.data_ptr()
         a.pre_eps = float(pre_eps)
         a.pre_gamma = _ptr(pre_gamma)
-        if pre_gamma is not None and not skip:
+        if x_norm is not None and not skip:
+            # the caller's own X_norm tensor: PreNorm runs as normalise-then-project and leaves X_norm there
+            if variant != "prenorm" or x_norm.shape != x.shape or x_norm.dtype != x.dtype or not x_norm.is_contiguous():
+                raise ValueError("x_norm must be a contiguous tensor like x, and only PreNorm takes one")
+            self._x_norm = x_norm
+            a.x_norm = x_norm.data_ptr()
+        elif pre_gamma is not None and not skip:
             self._x_norm = torch.empty_like(x)
             a.x_norm = self._x_norm.data_ptr()
         a.qk_eps = float(qk_eps)

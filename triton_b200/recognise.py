@@ -35,6 +35,15 @@ class Program:
     block_params: List[str]
     tensors: Set[str] = field(default_factory=set)
     n_kernels: int = 1
+    # What the candidate's loop / fusion structure selects in the CUDA backend's launch plan:
+    #   kernels            top-level statements = kernels the reference would launch (TritonGen.py:590)
+    #   in_memory          `tensor` temporaries the candidate keeps in memory between kernels or sloops
+    #   x_norm_in_memory   PreNorm: X_norm is stored by one kernel and loaded by another -> the backend runs
+    #                      normalise-then-project and fills the caller's X_norm; otherwise the row scale is
+    #                      folded into the projection's epilogue and X_norm never exists
+    #   scores_in_memory   the candidate materialises [H, M, P+M] score tensors (C, C_exp, ...): the backend
+    #                      never does (online softmax); those tensors are accepted and left untouched
+    schedule: Dict[str, object] = field(default_factory=dict)
 
 
 def _names(node: ASTNode) -> List[str]:
@@ -139,7 +148,9 @@ def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None) -> Pr
         variant = "roco"
     elif {"Q_norm", "K_norm"} & names:
         variant = "qknorm"
-    elif "X_norm" in names and has_attention:
+    elif ({"X_norm", "X2"} & names) and has_attention:
+        # X2 (row sums of squares of X) marks the candidates that normalise inside the projection loop and
+        # never name X_norm
         variant = "prenorm"
     elif has_attention:
         variant = "vanilla"
@@ -160,4 +171,13 @@ def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None) -> Pr
         if variant == "roco" and not {"C_out1", "C_out2"} <= stored:
             raise ValueError("RoCo IR must store C_out1 and C_out2")
     tensor_params = sorted(_memory_resident(accesses))
-    return Program(variant, tensor_params, sorted(blocks), names, len(kernels))
+    declared_io = {a.name for a in accesses if a.kind in (NodeType.INPUT, NodeType.OUTPUT)}
+    in_memory = sorted(n for n in tensor_params if n not in declared_io)
+    score_like = {"C", "C_exp", "C_div", "C_sum", "C_perturb", "C_exp_perturb", "C_sum_perturb", "C_div_perturb"}
+    schedule = {
+        "kernels": len(kernels),
+        "in_memory": in_memory,
+        "x_norm_in_memory": variant == "prenorm" and "X_norm" in tensor_params,
+        "scores_in_memory": sorted(score_like & set(tensor_params)),
+    }
+    return Program(variant, tensor_params, sorted(blocks), names, len(kernels), schedule)

@@ -87,6 +87,10 @@ class BoundOperator:
                   wv=t["WV"], causal=self.causal, scale=self.scale, pre_eps=self.eps, qk_eps=self.eps,
                   pre_gamma=t.get("gamma"), gamma_q=t.get("gamma_q"), gamma_k=t.get("gamma_k"),
                   single_p=self.single_p)
+        if self.variant == "prenorm" and "X_norm" in t:
+            # the program keeps X_norm in memory (a kernel of its own stores it): same schedule here, and the
+            # caller's tensor receives the normalised rows as it would from the generated kernels
+            kw["x_norm"] = t["X_norm"].reshape(B * M, self.N)
         if self.variant == "keyformer":
             noise = t.get("noise")
             mode = self.noise_mode if noise is None or self.noise_mode == L.TRN_NOISE_GUMBEL else L.TRN_NOISE_TENSOR
