@@ -448,7 +448,7 @@ int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream) {
     struct SplitGuard {
       explicit SplitGuard(int n) { tls_attn_split_override = n; }
       ~SplitGuard() { tls_attn_split_override = 0; }
-    } guard(attn_planned_splits(d.B, d.M, d.P, d.Hq, d.Hkv, d.D, ds->sm_count));
+    } guard(attn_planned_splits(d.B, d.M, d.P, d.Hq, d.Hkv, d.D, d.causal, ds->sm_count));
     const size_t esz = 2;
     const size_t stat_esz = d.stats_fp32 ? 4 : 2;
     const size_t x_item = a->x_bytes / d.B, o_item = a->o_bytes / d.B;

@@ -693,8 +693,10 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (ctas > 0x7fffffffLL) return TRN_E_SHAPE;
   // split-KV when the launch would leave most SMs idle and the caller lent scratch for the partials
   const long long rows = static_cast<long long>(a.B) * a.Hq * a.M;
+  // under a causal mask a tile sees on average the prefix plus half of the new keys
+  const int l_eff = a.causal ? a.P + (a.M + 1) / 2 : L;
   int n_splits = tls_attn_split_override > 0 ? tls_attn_split_override
-                                             : attn_split_count(static_cast<int>(ctas), L, ds.sm_count);
+                                             : attn_split_count(static_cast<int>(ctas), l_eff, ds.sm_count);
   if (n_splits > (L + BKV - 1) / BKV) n_splits = 1;
   if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0) n_splits = 1;
   while (n_splits > 1 && split_bytes(n_splits, rows, D, MODE == 0) > a.workspace_bytes) --n_splits;
@@ -750,17 +752,17 @@ int attn_split_count(int ctas, int L, int sm_count) {
 
 thread_local int tls_attn_split_override = 0;
 
-int attn_planned_splits(int B, int M, int P, int Hq, int Hkv, int D, int sm_count) {
+int attn_planned_splits(int B, int M, int P, int Hq, int Hkv, int D, int causal, int sm_count) {
   if (B <= 0 || M <= 0 || P < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || (D != 64 && D != 128)) return 1;
   const int group = Hq / Hkv;
   const long long n_qb = (M + BQ - 1) / BQ;
   const long long ctas = group >= 2 ? n_qb * B * Hkv * ((group + 1) / 2) : ((n_qb + 1) / 2) * B * Hq;
   if (ctas > sm_count) return 1;
-  return attn_split_count(static_cast<int>(ctas), P + M, sm_count);
+  return attn_split_count(static_cast<int>(ctas), causal ? P + (M + 1) / 2 : P + M, sm_count);
 }
 
 size_t attn_split_workspace(int B, int M, int P, int Hq, int Hkv, int D, int sm_count) {
-  const int n = attn_planned_splits(B, M, P, Hq, Hkv, D, sm_count);
+  const int n = attn_planned_splits(B, M, P, Hq, Hkv, D, /*causal=*/0, sm_count);     // the larger of the two cases
   if (n <= 1) return 0;
   return split_bytes(n, static_cast<long long>(B) * Hq * M, D, true);
 }

@@ -55,7 +55,7 @@ constexpr int kAttnNominalSMs = 148;     // sizing only: the launch itself uses 
 int attn_split_count(int ctas, int L, int sm_count);
 size_t attn_split_workspace(int B, int M, int P, int Hq, int Hkv, int D, int sm_count);
 // the split count a launch of this shape picks when its workspace is large enough
-int attn_planned_splits(int B, int M, int P, int Hq, int Hkv, int D, int sm_count);
+int attn_planned_splits(int B, int M, int P, int Hq, int Hkv, int D, int causal, int sm_count);
 // > 0: attention launches made by this thread use exactly this many splits (workspace permitting) instead
 // of their own choice; set by callers that cut one problem into several launches and want each output
 // element computed as the uncut launch would
