@@ -276,13 +276,16 @@ def run_ours(args, w):
                 xin, kw["wq"], kw["wk"], kw["wv"], q=qv, k_cache=kv_, v_cache=vv, B=B, M=S, P=0, Hq=Hq, Hkv=Hkv, D=D,
                 qk_norm=variant == "qknorm", qk_eps=1e-5, gamma_q=kw.get("gamma_q"), gamma_k=kw.get("gamma_k"))))
         lse = torch.empty(B, Hq, S, device=dev)
-        stages.append(("attention", lambda: ops.attention(qv, kv_, vv, ov, P=0, causal=True, scale=sc, lse=lse)))
         if variant == "keyformer":
+            # one pass: attention output, lse and the perturbed scores' lse (as the block runs it)
             lse_p = torch.empty_like(lse)
-            stages.append(("perturbed_lse", lambda: ops.attention(qv, kv_, vv, None, P=0, causal=True, scale=sc, lse=lse_p,
-                                                                  noise_mode=L.TRN_NOISE_GUMBEL, tau=1.0, seed=0)))
+            stages.append(("attention+perturbed_lse", lambda: ops.attention(
+                qv, kv_, vv, ov, P=0, causal=True, scale=sc, lse=lse, lse_pert=lse_p, noise_mode=L.TRN_NOISE_GUMBEL,
+                tau=1.0, seed=0)))
             stages.append(("colstats", lambda: ops.attn_colstats(qv, kv_, lse_p, sp, None, P=0, causal=True, scale=sc,
                                                                  noise_mode=L.TRN_NOISE_GUMBEL, tau=1.0, seed=0)))
+        else:
+            stages.append(("attention", lambda: ops.attention(qv, kv_, vv, ov, P=0, causal=True, scale=sc, lse=lse)))
         if variant == "roco":
             stages.append(("colstats", lambda: ops.attn_colstats(qv, kv_, lse, sp, sp2, P=0, causal=True, scale=sc)))
         if idx is not None:

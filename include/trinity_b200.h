@@ -149,6 +149,15 @@ typedef struct {
                             CTAs (split-KV) and merges their partial results with a second small kernel; the
                             result is the same softmax.  Contents need not be initialised.               */
   size_t workspace_bytes; /* a smaller area than trinity_attention_workspace() asks for means fewer splits */
+  float* lse_pert;       /* with noise_mode != NONE: when given, ONE pass computes the attention output o, lse of
+                            the plain scores (if `lse` is given) and, here, lse of the perturbed scores
+                            [B, Hq, M]; when NULL the call is the perturbed-lse-only pass described above    */
+  float* scores;         /* optional fp32 [B, Hq, M, score_pitch]: every score the pass sees, in the base-2 log
+                            domain (perturbed scores when noise_mode != NONE, else scale * s * log2 e; keys
+                            a causal row must not see are -inf).  Lets small problems compute the per-key
+                            statistics from memory instead of a second q k^T pass (the schedule of the
+                            reference's programs that keep C_exp / C_exp_perturb in memory)               */
+  int64_t score_pitch;   /* elements per (b, h, query) row of `scores`: a multiple of 32, >= P + M */
 } TrnAttnArgs;
 int trinity_attention(const TrnAttnArgs* a, void* cuda_stream);
 /* Scratch that makes split-KV possible for this shape (0: the launch would not split).  No reference
@@ -179,6 +188,12 @@ typedef struct {
   const void* noise;
   int64_t noise_stride_b, noise_stride_h, noise_stride_i;
   uint64_t seed;
+  const float* scores;   /* optional: the scores trinity_attention kept (TrnAttnArgs.scores, same pitch).  With them
+                            the statistics are summed from memory: q, k_cache, scale, tau and the noise fields are
+                            not used (noise is already in the scores; `causal` and P still say which scores
+                            exist), `lse` must be the
+                            log-sum-exp that belongs to those scores                                        */
+  int64_t score_pitch;
 } TrnColStatsArgs;
 int trinity_attn_colstats(const TrnColStatsArgs* a, void* cuda_stream);
 

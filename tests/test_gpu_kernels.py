@@ -300,3 +300,55 @@ def test_mma_rate_probe_reports_plausible_clocks():
     # twice the columns never cost less than half as much again per instruction
     assert rows["SS N256"]["clk_per_mma"] >= rows["SS N128"]["clk_per_mma"]
     assert rows["SS N256"]["mac_per_clk_per_sm"] <= 4096 * 1.05     # the nominal dense bf16 rate per SM
+
+
+@pytest.mark.parametrize("B,M,P,Hq,Hkv,D,dt,causal,noise_mode", (
+    (1, 16, 1024, 8, 8, 128, HF, False, L.TRN_NOISE_TENSOR),      # the reference's shape (split-KV with a workspace)
+    (2, 200, 72, 6, 2, 64, BF, True, L.TRN_NOISE_GUMBEL),
+    (1, 300, 0, 4, 4, 128, BF, True, L.TRN_NOISE_TENSOR),
+))
+def test_fused_attention_and_perturbed_lse_equals_two_passes_and_kept_scores_give_the_same_statistics(
+        B, M, P, Hq, Hkv, D, dt, causal, noise_mode):
+    """One pass (o, lse, perturbed lse, scores kept) against the two separate passes, and per-key statistics summed
+    from the kept scores against the recomputing kernel."""
+    scale, tau, seed = D ** -0.5, 1.5, 5
+    L_ = P + M
+    q, kc, vc = _attn_inputs(B, M, P, Hq, Hkv, D, dt, seed=21)
+    torch.manual_seed(22)
+    noise = torch.randn(B, Hq, M, L_).to(dt).cuda() if noise_mode == L.TRN_NOISE_TENSOR else None
+    qv, kv, vv = ops.as_bshd(q.cuda(), "bshd"), ops.as_bshd(kc.cuda(), "bhsd"), ops.as_bshd(vc.cuda(), "bhsd")
+    kw = dict(P=P, causal=causal, scale=scale)
+    nkw = dict(noise_mode=noise_mode, tau=tau, noise=noise, seed=seed)
+    # two passes
+    o_a = torch.zeros(B, M, Hq, D, device="cuda", dtype=dt)
+    lse_a, lse2_a = torch.zeros(B, Hq, M, device="cuda"), torch.zeros(B, Hq, M, device="cuda")
+    ops.attention(qv, kv, vv, o_a, lse=lse_a, **kw)
+    ops.attention(qv, kv, vv, None, lse=lse2_a, **kw, **nkw)
+    sp_a, sp_r, sp2_r = (torch.zeros(B, Hq, L_, device="cuda") for _ in range(3))
+    ops.attn_colstats(qv, kv, lse2_a, sp_a, None, **kw, **nkw)
+    ops.attn_colstats(qv, kv, lse_a, sp_r, sp2_r, **kw)
+    for use_ws in (False, True):
+        nb = ops.attention_workspace_bytes(B, M, P, Hq, Hkv, D) if use_ws else 0
+        ws = torch.empty(nb, dtype=torch.uint8, device="cuda").fill_(0xff) if nb else None
+        pitch = (L_ + 31) // 32 * 32
+        o_b = torch.zeros_like(o_a)
+        lse_b, lse2_b = torch.zeros_like(lse_a), torch.zeros_like(lse_a)
+        sc = torch.full((B, Hq, M, pitch), float("nan"), device="cuda")
+        ops.attention(qv, kv, vv, o_b, lse=lse_b, lse_pert=lse2_b, scores=sc, workspace=ws, **kw, **nkw)
+        sp_b = torch.zeros_like(sp_a)
+        ops.attn_colstats(qv, kv, lse2_b, sp_b, None, scores=sc, **kw)
+        # plain scores kept by an un-noised pass, for the RoCo sums
+        sc0 = torch.full((B, Hq, M, pitch), float("nan"), device="cuda")
+        o_c, lse_c = torch.zeros_like(o_a), torch.zeros_like(lse_a)
+        ops.attention(qv, kv, vv, o_c, lse=lse_c, scores=sc0, workspace=ws, **kw)
+        sp_c, sp2_c = torch.zeros_like(sp_a), torch.zeros_like(sp_a)
+        ops.attn_colstats(qv, kv, lse_c, sp_c, sp2_c, scores=sc0, **kw)
+        torch.cuda.synchronize()
+        assert L.kernel_status() == 0
+        assert_parity(o_b, o_a.float().cpu(), "o fused vs separate")
+        assert (lse_b - lse_a).abs().max().item() <= 1e-4 and (lse2_b - lse2_a).abs().max().item() <= 1e-4
+        if not causal:          # under a causal mask the scores of keys a query must not see are never written
+            assert not torch.isnan(sc[..., :L_]).any() and not torch.isnan(sc0[..., :L_]).any()
+        assert_parity(sp_b, sp_a.cpu(), "KeyFormer sums from kept scores", abs_tol=1e-3 * max(1.0, M / 16), rel_tol=1e-3)
+        assert_parity(sp_c, sp_r.cpu(), "RoCo sum p from kept scores", abs_tol=1e-3 * max(1.0, M / 16), rel_tol=1e-3)
+        assert_parity(sp2_c, sp2_r.cpu(), "RoCo sum p^2 from kept scores", abs_tol=1e-3 * max(1.0, M / 16), rel_tol=1e-3)

@@ -63,6 +63,7 @@ class TrnAttnArgs(C.Structure):
         ("noise", C.c_void_p), ("noise_stride_b", C.c_int64), ("noise_stride_h", C.c_int64),
         ("noise_stride_i", C.c_int64), ("seed", C.c_uint64), ("single_p", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("lse_pert", C.c_void_p), ("scores", C.c_void_p), ("score_pitch", C.c_int64),
     ]
 
 
@@ -75,6 +76,7 @@ class TrnColStatsArgs(C.Structure):
         ("noise_mode", C.c_int), ("tau", C.c_float),
         ("noise", C.c_void_p), ("noise_stride_b", C.c_int64), ("noise_stride_h", C.c_int64),
         ("noise_stride_i", C.c_int64), ("seed", C.c_uint64),
+        ("scores", C.c_void_p), ("score_pitch", C.c_int64),
     ]
 
 

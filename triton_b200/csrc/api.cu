@@ -126,9 +126,15 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct BlockWorkspace {
   size_t row_scale_off, lse_off, lse2_off, split_off;
-  size_t required;   // the block cannot run with less
-  size_t total;      // required + the optional split-KV area of the attention launches
+  size_t split_bytes;   // optional: split-KV partials of the attention launch
+  size_t score_off, score_bytes, score_pitch;   // optional: scores kept for the per-key statistics (small problems)
+  size_t required;      // the block cannot run with less
+  size_t total;         // required + the optional areas
 };
+
+// KeyFormer / RoCo problems whose [B, Hq, M, P+M] fp32 scores fit in this many bytes keep them in memory and sum
+// the per-key statistics from there (one q k^T pass instead of two)
+constexpr size_t kKeepScoresMaxBytes = 32u << 20;
 
 BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
   BlockWorkspace w{};
@@ -143,7 +149,14 @@ BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
   off += align_up(lse * sizeof(float), 256);
   w.split_off = off;
   w.required = off;
-  w.total = off + attn_split_workspace(a.B, a.M, a.P, a.Hq, a.Hkv, a.D, kAttnNominalSMs);
+  w.split_bytes = attn_split_workspace(a.B, a.M, a.P, a.Hq, a.Hkv, a.D, kAttnNominalSMs);
+  off += w.split_bytes;
+  w.score_off = off;
+  w.score_pitch = (static_cast<size_t>(a.P) + a.M + 31) / 32 * 32;
+  const size_t sb = lse * w.score_pitch * sizeof(float);
+  const bool stats = (a.variant == TRN_KEYFORMER || a.variant == TRN_ROCO);
+  w.score_bytes = (stats && sb <= kKeepScoresMaxBytes) ? align_up(sb, 256) : 0;
+  w.total = off + w.score_bytes;
   return w;
 }
 
@@ -378,9 +391,27 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
   at.noise_mode = TRN_NOISE_NONE;
   at.tau = 1.0f;
   at.single_p = a->single_p;
-  // what the caller lent beyond the required part serves split-KV (both attention launches, in turn)
+  // What the caller lent beyond the required part: first the split-KV partials of the attention launch, then,
+  // for small KeyFormer / RoCo problems, the scores the statistics are summed from.
+  const bool keep_scores = stats && wl.score_bytes > 0 && a->workspace_bytes >= wl.score_off + wl.score_bytes;
   at.workspace = ws + wl.split_off;
-  at.workspace_bytes = a->workspace_bytes - wl.split_off;
+  at.workspace_bytes = keep_scores ? wl.split_bytes : a->workspace_bytes - wl.split_off;
+  if (keep_scores) {
+    at.scores = reinterpret_cast<float*>(ws + wl.score_off);
+    at.score_pitch = static_cast<int64_t>(wl.score_pitch);
+  }
+  if (a->variant == TRN_KEYFORMER) {
+    // the same pass also gives the log-sum-exp of the perturbed scores (ref_rms.py:172,174)
+    if (a->noise_mode == TRN_NOISE_NONE) return TRN_E_VARIANT;
+    at.noise_mode = a->noise_mode;
+    at.tau = a->tau;
+    at.noise = a->noise;
+    at.noise_stride_b = a->noise_stride_b;
+    at.noise_stride_h = a->noise_stride_h;
+    at.noise_stride_i = a->noise_stride_i;
+    at.seed = a->seed;
+    at.lse_pert = lse_pert;
+  }
   rc = launch_attention(at, st, *ds);
   if (rc != TRN_OK) return rc;
 
@@ -388,19 +419,6 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
     const float* lse_for_stats = lse;
     int noise_mode = TRN_NOISE_NONE;
     if (a->variant == TRN_KEYFORMER) {
-      // second row pass: log-sum-exp of the perturbed scores (ref_rms.py:172,174)
-      TrnAttnArgs pt = at;
-      pt.lse = lse_pert;
-      pt.noise_mode = a->noise_mode;
-      pt.tau = a->tau;
-      pt.noise = a->noise;
-      pt.noise_stride_b = a->noise_stride_b;
-      pt.noise_stride_h = a->noise_stride_h;
-      pt.noise_stride_i = a->noise_stride_i;
-      pt.seed = a->seed;
-      if (pt.noise_mode == TRN_NOISE_NONE) return TRN_E_VARIANT;
-      rc = launch_attention(pt, st, *ds);
-      if (rc != TRN_OK) return rc;
       lse_for_stats = lse_pert;
       noise_mode = a->noise_mode;
     }
@@ -422,9 +440,13 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
     cs.noise_stride_h = a->noise_stride_h;
     cs.noise_stride_i = a->noise_stride_i;
     cs.seed = a->seed;
+    if (keep_scores) {
+      cs.scores = at.scores;
+      cs.score_pitch = at.score_pitch;
+    }
     rc = launch_colstats(cs, st, *ds);
     if (rc != TRN_OK) return rc;
-  }
+    }
   return TRN_OK;
 }
 

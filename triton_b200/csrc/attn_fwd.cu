@@ -19,7 +19,10 @@
 //               product carries ~16 mantissa bits of p.  O is rescaled in TMEM only when a row's max
 //               grew by more than 2^8 since the last rescale.
 // MODE 1 (KeyFormer's second row pass, ref_rms.py:172-174) computes only the log-sum-exp of the
-// perturbed scores (s + g) / tau and skips P, v and O.
+// perturbed scores (s + g) / tau and skips P, v and O.  MODE 2 does both in one pass over the scores: the
+// attention output and, from the same S tile while it is in registers, the perturbed log-sum-exp.
+// Optionally every (perturbed) score is also written out in the log2 domain, so that for small problems the
+// per-key statistics need no second q k^T pass.
 //
 // Algorithmic flops per launch (MODE 0): 4 * B * Hq * D * (number of visible (query, key) pairs).
 #include <math.h>
@@ -43,6 +46,9 @@ struct AttnParams {
   void* o;
   long long o_sb, o_ss, o_sh;
   float* lse;
+  float* lse_pert;     // MODE 2: log-sum-exp of the perturbed scores (MODE 1 writes it to `lse`)
+  float* scores;       // optional [B, Hq, M, score_pitch] fp32: every score in the log2 domain (perturbed in MODE 1 / 2)
+  int score_pitch;     // multiple of 32
   int B, M, P, L, Hq, Hkv, group;
   int n_qblocks;       // 128-row query blocks
   int pair_heads;      // 1: tiles = two heads of a kv group; 0: tiles = two consecutive query blocks
@@ -59,6 +65,7 @@ struct AttnParams {
   int ctas_per_split;
   float* part_o;       // [n_splits, B, Hq, M, D]
   float* part_lse;     // [n_splits, B, Hq, M]
+  float* part_lse2;    // MODE 2: the same for the perturbed scores
   int* status;
 };
 
@@ -87,6 +94,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
   using SM = AttnSmem<D>;
   constexpr int KS = SM::kStages;
+  // MODE 0: attention; 1: perturbed log-sum-exp only; 2: both in one pass; 3: attention that also keeps its scores
+  constexpr bool kHasPV = (MODE != 1);                 // P, v and O exist
+  constexpr bool kPert = (MODE == 1 || MODE == 2);     // perturbed log-sum-exp wanted
+  constexpr bool kDump = (MODE == 3);                  // plain scores written out
   __shared__ int s_skip;
   if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(p.status);
   __syncthreads();
@@ -198,7 +209,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
-      if (MODE == 0) tma_prefetch_desc(&tm_v);
+      if (kHasPV) tma_prefetch_desc(&tm_v);
       const int n_tiles = (tile[0].n_blocks ? 1 : 0) + (tile[1].n_blocks ? 1 : 0);
       mbar_expect_tx(q_full, n_tiles * SM::kTileBytes);
 #pragma unroll
@@ -221,7 +232,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < SM::kChunks; ++c)
           tma_load_head_tile(k_s(st) + c * SM::kChunkBytes, &tm_k, k_full(st), p.ki, c * 64, (j0 + j) * BKV, kvh, b);
-        if (MODE == 0) {
+        if (kHasPV) {
           mbar_expect_tx(v_full(st), SM::kTileBytes);
 #pragma unroll
           for (int c = 0; c < SM::kChunks; ++c)
@@ -268,7 +279,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool k_next_ready = false;
       for (int t = 0; t < 2 && ok; ++t) {
         if (j >= tile[t].n_blocks) continue;
-        if (MODE == 0) {
+        if (kHasPV) {
           bool w = mbar_wait(v_full(st), ph, ctl, KST_TIMEOUT_MMA);
           ok = __all_sync(0xffffffffu, w);
           if (!ok) break;
@@ -331,6 +342,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int h = tile[t].h;
     const int n_blocks = tile[t].n_blocks;
     const bool row_valid = q_abs < p.M;
+    // a warp whose 32 rows all lie past the last query (M = 16 new tokens fill half of one warp) only keeps
+    // the barrier protocol going: its rows of S / P / O are never stored and feed no other row
+    const bool warp_active = tile[t].q0 + quad * 32 < p.M;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int limit = p.causal ? min(p.P + q_abs, p.L - 1) : p.L - 1;               // last visible key of this row
     const int limit_min = p.causal ? min(p.P + tile[t].q0, p.L - 1) : p.L - 1;     // ... of the tile's first row
@@ -340,9 +354,99 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = true;
     uint32_t r[32];
     const uint32_t rowhash =
-        (MODE == 1) ? noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)),
-                                    static_cast<uint32_t>(q_abs))
-                    : 0u;
+        kPert ? noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)),
+                              static_cast<uint32_t>(q_abs))
+              : 0u;
+    // state of the perturbed log-sum-exp, and where this row's scores go when they are kept
+    float m2_run = -INFINITY, l2_run = 0.f;
+    float* score_row = (p.scores != nullptr && row_valid)
+                           ? p.scores + ((static_cast<long long>(b) * p.Hq + h) * p.M + q_abs) * p.score_pitch
+                           : nullptr;
+    // Perturbed scores of chunk c of block kv0 (S values in r[]): online log-sum-exp update, optional write-out.
+    // t = (s * scale + g) * log2(e) / tau; with generated noise g = -ln2 * log2(E):  t = s * c_s + log2(E) * c_g
+    auto pert_chunk = [&](int kv0, int c, bool masked) {
+      const bool fast = !masked && p.noise.mode == TRN_NOISE_GUMBEL;
+      // 128-bit loads need the noise rows 16-byte aligned (checked once on the host)
+      const bool fast_tensor = !masked && p.noise.mode == TRN_NOISE_TENSOR && p.noise_vec_ok;
+      const float c_s = p.scale * p.pert_log2;
+      const float c_g = -0.6931471805599453f * p.pert_log2;
+      float tv[32];
+      float cm = -INFINITY;
+      if (fast) {
+        // interior block, generated noise: no per-element compare, hash advanced by one add per key
+        uint32_t jc = static_cast<uint32_t>(kv0 + c * 32) * 0x85ebca6bu;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          uint32_t x = rowhash ^ jc;
+          jc += 0x85ebca6bu;
+          x ^= x >> 16; x *= 0x7feb352du;
+          x ^= x >> 15;
+          const float v = fmaf(gumbel_log2e_from_bits(x), c_g, __uint_as_float(r[i]) * c_s);
+          tv[i] = v;
+          cm = fmaxf(cm, v);
+        }
+      } else if (fast_tensor) {
+        // interior block, noise tensor: this row's 32 values come in as four 128-bit loads
+        const T* nrow = static_cast<const T*>(p.noise.ptr) + b * p.noise.sb + h * p.noise.sh +
+                        static_cast<long long>(row_valid ? q_abs : 0) * p.noise.si + kv0 + c * 32;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          const uint4 nv = __ldg(reinterpret_cast<const uint4*>(nrow + i));
+          const uint32_t w4[4] = {nv.x, nv.y, nv.z, nv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 g2 = Io<T>::unpack2(w4[e]);
+            const float v0 = (__uint_as_float(r[i + 2 * e]) * p.scale + g2.x) * p.pert_log2;
+            const float v1 = (__uint_as_float(r[i + 2 * e + 1]) * p.scale + g2.y) * p.pert_log2;
+            tv[i + 2 * e] = v0;
+            tv[i + 2 * e + 1] = v1;
+            cm = fmax3(cm, v0, v1);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = kv0 + c * 32 + i;
+          float v = -INFINITY;
+          if (col <= limit) {
+            const float g = row_valid ? noise_at<T>(p.noise, rowhash, b, h, q_abs, col) : 0.f;
+            v = (__uint_as_float(r[i]) * p.scale + g) * p.pert_log2;
+          }
+          tv[i] = v;
+          cm = fmaxf(cm, v);
+        }
+      }
+      const float m_new = fmaxf(m2_run, cm);
+      if (m_new != -INFINITY) {
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc += ex2_approx(tv[i] - m_new);
+        l2_run = l2_run * ex2_approx(m2_run - m_new) + acc;
+        m2_run = m_new;
+      }
+      if (score_row != nullptr && kv0 + c * 32 < p.score_pitch) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(score_row + kv0 + c * 32 + i) = make_float4(tv[i], tv[i + 1], tv[i + 2], tv[i + 3]);
+      }
+    };
+    // plain scores of chunk c (S values in r[]) written out in the log2 domain; keys past a row's limit as -inf
+    auto dump_chunk = [&](int kv0, int c, bool masked) {
+      if (score_row == nullptr || kv0 + c * 32 >= p.score_pitch) return;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float4 v = make_float4(__uint_as_float(r[i]) * p.scale_log2, __uint_as_float(r[i + 1]) * p.scale_log2,
+                               __uint_as_float(r[i + 2]) * p.scale_log2, __uint_as_float(r[i + 3]) * p.scale_log2);
+        if (masked) {
+          const int col = kv0 + c * 32 + i;
+          if (col > limit) v.x = -INFINITY;
+          if (col + 1 > limit) v.y = -INFINITY;
+          if (col + 2 > limit) v.z = -INFINITY;
+          if (col + 3 > limit) v.w = -INFINITY;
+        }
+        *reinterpret_cast<float4*>(score_row + kv0 + c * 32 + i) = v;
+      }
+    };
 
     for (int j = 0; j < n_blocks; ++j) {
       const int kv0 = (j0 + j) * BKV;
@@ -350,73 +454,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (!warp_active) {
+        if (kHasPV) mbar_arrive(p_ready(t, 0));
+        mbar_arrive(p_ready(t, 1));
+        continue;
+      }
       const bool masked = (kv0 + BKV - 1) > limit_min;
 
       if (MODE == 1) {
         // one pass, chunk-wise online log-sum-exp of the perturbed scores
-        const bool fast = !masked && p.noise.mode == TRN_NOISE_GUMBEL;
-        // 128-bit loads need the noise rows 16-byte aligned (checked once on the host)
-        const bool fast_tensor = !masked && p.noise.mode == TRN_NOISE_TENSOR && p.noise_vec_ok;
-        // t = (s * scale + g) * log2(e) / tau with g = -ln2 * log2(E):  t = s * c_s + log2(E) * c_g
-        const float c_s = p.scale * p.pert_log2;
-        const float c_g = -0.6931471805599453f * p.pert_log2;
+#pragma unroll 1
         for (int c = 0; c < BKV / 32; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
-          float tv[32];
-          float cm = -INFINITY;
-          if (fast) {
-            // interior block, generated noise: no per-element compare, hash advanced by one add per key
-            uint32_t jc = static_cast<uint32_t>(kv0 + c * 32) * 0x85ebca6bu;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              uint32_t x = rowhash ^ jc;
-              jc += 0x85ebca6bu;
-              x ^= x >> 16; x *= 0x7feb352du;
-              x ^= x >> 15;
-              const float v = fmaf(gumbel_log2e_from_bits(x), c_g, __uint_as_float(r[i]) * c_s);
-              tv[i] = v;
-              cm = fmaxf(cm, v);
-            }
-          } else if (fast_tensor) {
-            // interior block, noise tensor: this row's 32 values come in as four 128-bit loads
-            const T* nrow = static_cast<const T*>(p.noise.ptr) + b * p.noise.sb + h * p.noise.sh +
-                            static_cast<long long>(row_valid ? q_abs : 0) * p.noise.si + kv0 + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              const uint4 nv = __ldg(reinterpret_cast<const uint4*>(nrow + i));
-              const uint32_t w4[4] = {nv.x, nv.y, nv.z, nv.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 g2 = Io<T>::unpack2(w4[e]);
-                const float v0 = (__uint_as_float(r[i + 2 * e]) * p.scale + g2.x) * p.pert_log2;
-                const float v1 = (__uint_as_float(r[i + 2 * e + 1]) * p.scale + g2.y) * p.pert_log2;
-                tv[i + 2 * e] = v0;
-                tv[i + 2 * e + 1] = v1;
-                cm = fmax3(cm, v0, v1);
-              }
-            }
-          } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = kv0 + c * 32 + i;
-            float v = -INFINITY;
-            if (col <= limit) {
-              const float g = row_valid ? noise_at<T>(p.noise, rowhash, b, h, q_abs, col) : 0.f;
-              v = (__uint_as_float(r[i]) * p.scale + g) * p.pert_log2;
-            }
-            tv[i] = v;
-            cm = fmaxf(cm, v);
-          }
-          }
-          const float m_new = fmaxf(m_run, cm);
-          if (m_new != -INFINITY) {
-            float acc = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc += ex2_approx(tv[i] - m_new);
-            l_run = l_run * ex2_approx(m_run - m_new) + acc;
-            m_run = m_new;
-          }
+          pert_chunk(kv0, c, masked);
         }
         tc_fence_before();
         mbar_arrive(p_ready(t, 1));
@@ -425,7 +476,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       // ---- pass 1: block maximum of this row
       float mb = -INFINITY;
-      if (masked) {
+      if constexpr (kPert || kDump) {
+        // one loop with one call site of the perturbed-score code: this variant's instruction footprint matters
+        // when the projection's weights have just swept the L2 (the reference's M = 16 shapes)
+#pragma unroll 1
+        for (int c = 0; c < BKV / 32; ++c) {
+          tmem_ld32(s_tmem + c * 32, r);
+          tmem_wait_ld();
+          if (masked) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (kv0 + c * 32 + i <= limit) mb = fmaxf(mb, __uint_as_float(r[i]));
+          } else {
+            float m0 = fmaxf(__uint_as_float(r[0]), __uint_as_float(r[1]));
+            float m1 = fmaxf(__uint_as_float(r[2]), __uint_as_float(r[3]));
+#pragma unroll
+            for (int i = 4; i < 32; i += 4) {
+              m0 = fmax3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+              m1 = fmax3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+            }
+            mb = fmax3(mb, m0, m1);
+          }
+          if constexpr (kPert) pert_chunk(kv0, c, masked);
+          else dump_chunk(kv0, c, masked);
+        }
+      } else if (masked) {
         for (int c = 0; c < BKV / 32; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
@@ -525,7 +600,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool split_out = p.n_splits > 1;
     const long long part_row =
         ((static_cast<long long>(split) * p.B + b) * p.Hq + h) * p.M + q_abs;   // row of the partial results
-    if (ok && MODE == 0 && n_blocks > 0) {
+    if (MODE == 1) { m_run = m2_run; l_run = l2_run; }        // MODE 1 reports the perturbed value as its lse
+    if (ok && kHasPV && n_blocks > 0 && warp_active) {
       ok = mbar_wait(pv_done(t), (n_blocks - 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
@@ -561,10 +637,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (split_out) {
       // a CTA whose key range misses this tile contributes weight 0
-      if (ok && tile[t].present && row_valid)
+      if (ok && tile[t].present && row_valid) {
         p.part_lse[part_row] = (n_blocks > 0) ? m_run + log2f(l_run) : -INFINITY;
-    } else if (ok && n_blocks > 0 && row_valid && p.lse != nullptr) {
-      p.lse[(static_cast<long long>(b) * p.Hq + h) * p.M + q_abs] = m_run + log2f(l_run);
+        if (MODE == 2) p.part_lse2[part_row] = (n_blocks > 0) ? m2_run + log2f(l2_run) : -INFINITY;
+      }
+    } else if (ok && n_blocks > 0 && row_valid) {
+      const long long li = (static_cast<long long>(b) * p.Hq + h) * p.M + q_abs;
+      if (p.lse != nullptr) p.lse[li] = m_run + log2f(l_run);
+      if (MODE == 2) p.lse_pert[li] = m2_run + log2f(l2_run);
     }
   }
 
@@ -586,7 +666,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
 attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, T* __restrict__ o,
-                    long long o_sb, long long o_ss, long long o_sh, float* __restrict__ lse_out, int n_splits, int B,
+                    long long o_sb, long long o_ss, long long o_sh, float* __restrict__ lse_out,
+                    const float* __restrict__ part_lse2, float* __restrict__ lse2_out, int n_splits, int B,
                     int Hq, int M, const int* __restrict__ status) {
   if (*reinterpret_cast<const volatile int*>(status) != 0) return;
   constexpr int VPL = D / 32;
@@ -633,12 +714,25 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     }
   }
   if (lse_out != nullptr && lane == 0) lse_out[row] = m + log2f(tot);
+  if (part_lse2 != nullptr && lane == 0) {       // the perturbed scores' log-sum-exp merges the same way
+    float m2 = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m2 = fmaxf(m2, part_lse2[s * rows + row]);
+    float t2 = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ls = part_lse2[s * rows + row];
+      if (ls != -INFINITY) t2 += ex2_approx(ls - m2);
+    }
+    lse2_out[row] = m2 + log2f(t2);
+  }
 }
 
+// layout: lse partials, second lse partials (always reserved, used by MODE 2), then o partials
+size_t split_lse_bytes(int n_splits, long long rows) {
+  return (static_cast<size_t>(n_splits) * rows * sizeof(float) + 255) / 256 * 256;
+}
 size_t split_bytes(int n_splits, long long rows, int D, bool with_o) {
   const size_t o_b = with_o ? (static_cast<size_t>(n_splits) * rows * D * sizeof(float) + 255) / 256 * 256 : 0;
-  const size_t l_b = (static_cast<size_t>(n_splits) * rows * sizeof(float) + 255) / 256 * 256;
-  return o_b + l_b;
+  return o_b + 2 * split_lse_bytes(n_splits, rows);
 }
 
 template <typename T, int D, int MODE, bool SPLIT>
@@ -651,7 +745,7 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (rc != TRN_OK) return rc;
   rc = make_head_tmap(&tm_k, &p.ki, a.k_cache, L, a.Hkv, a.B, D, BKV);
   if (rc != TRN_OK) return rc;
-  if (MODE == 0) {
+  if (MODE != 1) {
     rc = make_head_tmap(&tm_v, &p.vi, a.v_cache, L, a.Hkv, a.B, D, BKV);
     if (rc != TRN_OK) return rc;
   } else {
@@ -661,6 +755,9 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   p.o = a.o.ptr;
   p.o_sb = a.o.stride_b; p.o_ss = a.o.stride_s; p.o_sh = a.o.stride_h;
   p.lse = a.lse;
+  p.lse_pert = a.lse_pert;
+  p.scores = a.scores;
+  p.score_pitch = static_cast<int>(a.score_pitch);
   p.B = a.B; p.M = a.M; p.P = a.P; p.L = L; p.Hq = a.Hq; p.Hkv = a.Hkv; p.group = a.Hq / a.Hkv;
   p.n_qblocks = (a.M + BQ - 1) / BQ;
   p.pair_heads = p.group >= 2 ? 1 : 0;
@@ -699,14 +796,15 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
                                              : attn_split_count(static_cast<int>(ctas), l_eff, ds.sm_count);
   if (n_splits > (L + BKV - 1) / BKV) n_splits = 1;
   if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0) n_splits = 1;
-  while (n_splits > 1 && split_bytes(n_splits, rows, D, MODE == 0) > a.workspace_bytes) --n_splits;
+  while (n_splits > 1 && split_bytes(n_splits, rows, D, MODE != 1) > a.workspace_bytes) --n_splits;
   p.n_splits = n_splits;
   p.ctas_per_split = static_cast<int>(ctas);
   if (n_splits > 1) {
     uint8_t* ws = static_cast<uint8_t*>(a.workspace);
-    const size_t l_b = split_bytes(n_splits, rows, D, false);
+    const size_t l_b = split_lse_bytes(n_splits, rows);
     p.part_lse = reinterpret_cast<float*>(ws);
-    p.part_o = (MODE == 0) ? reinterpret_cast<float*>(ws + l_b) : nullptr;
+    p.part_lse2 = reinterpret_cast<float*>(ws + l_b);
+    p.part_o = (MODE != 1) ? reinterpret_cast<float*>(ws + 2 * l_b) : nullptr;
   }
   kern<<<static_cast<int>(ctas * n_splits), kAttnThreads, SM::kTotal, st>>>(tm_q, tm_k, tm_v, p);
   TRN_CUDA_TRY(cudaGetLastError());
@@ -714,8 +812,8 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
     const int warps_per_cta = 8;
     const long long cgrid = (rows + warps_per_cta - 1) / warps_per_cta;
     attn_combine_kernel<T, D><<<static_cast<int>(cgrid), warps_per_cta * 32, 0, st>>>(
-        p.part_o, p.part_lse, static_cast<T*>(a.o.ptr), a.o.stride_b, a.o.stride_s, a.o.stride_h, a.lse, n_splits,
-        a.B, a.Hq, a.M, ds.status);
+        p.part_o, p.part_lse, static_cast<T*>(a.o.ptr), a.o.stride_b, a.o.stride_s, a.o.stride_h, a.lse,
+        MODE == 2 ? p.part_lse2 : nullptr, a.lse_pert, n_splits, a.B, a.Hq, a.M, ds.status);
     TRN_CUDA_TRY(cudaGetLastError());
   }
   return TRN_OK;
@@ -724,12 +822,19 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
 template <typename T>
 int launch_typed(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   const bool pert = a.noise_mode != TRN_NOISE_NONE;
+  const bool fused = pert && a.lse_pert != nullptr;     // attention and the perturbed log-sum-exp in one pass
   if (a.D == 128) {
+    if (fused) return a.single_p ? launch_inst<T, 128, 2, false>(a, st, ds) : launch_inst<T, 128, 2, true>(a, st, ds);
     if (pert) return launch_inst<T, 128, 1, false>(a, st, ds);
+    if (a.scores != nullptr)
+      return a.single_p ? launch_inst<T, 128, 3, false>(a, st, ds) : launch_inst<T, 128, 3, true>(a, st, ds);
     return a.single_p ? launch_inst<T, 128, 0, false>(a, st, ds) : launch_inst<T, 128, 0, true>(a, st, ds);
   }
   if (a.D == 64) {
+    if (fused) return a.single_p ? launch_inst<T, 64, 2, false>(a, st, ds) : launch_inst<T, 64, 2, true>(a, st, ds);
     if (pert) return launch_inst<T, 64, 1, false>(a, st, ds);
+    if (a.scores != nullptr)
+      return a.single_p ? launch_inst<T, 64, 3, false>(a, st, ds) : launch_inst<T, 64, 3, true>(a, st, ds);
     return a.single_p ? launch_inst<T, 64, 0, false>(a, st, ds) : launch_inst<T, 64, 0, true>(a, st, ds);
   }
   return TRN_E_SHAPE;
@@ -775,13 +880,18 @@ int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& d
   if (a.noise_mode < TRN_NOISE_NONE || a.noise_mode > TRN_NOISE_GUMBEL) return TRN_E_VARIANT;
   if (a.q.ptr == nullptr || a.k_cache.ptr == nullptr) return TRN_E_NULL;
   if (!ht_ok(a.q) || !ht_ok(a.k_cache)) return TRN_E_ALIGN;
-  if (!pert) {
+  const bool fused = pert && a.lse_pert != nullptr;
+  if (!pert || fused) {
     if (a.v_cache.ptr == nullptr || a.o.ptr == nullptr) return TRN_E_NULL;
     if (!ht_ok(a.v_cache) || !ht_ok(a.o)) return TRN_E_ALIGN;
-  } else {
-    if (a.lse == nullptr) return TRN_E_NULL;
+  }
+  if (pert) {
+    if (!fused && a.lse == nullptr) return TRN_E_NULL;
     if (!(a.tau > 0.f)) return TRN_E_SHAPE;
     if (a.noise_mode == TRN_NOISE_TENSOR && a.noise == nullptr) return TRN_E_NULL;
+  }
+  if (a.scores != nullptr) {
+    if (a.score_pitch < a.P + a.M || (a.score_pitch & 31) != 0 || !aligned16(a.scores)) return TRN_E_SHAPE;
   }
   if (a.dtype == TRN_BF16) return launch_typed<__nv_bfloat16>(a, st, ds);
   if (a.dtype == TRN_FP16) return launch_typed<__half>(a, st, ds);

@@ -246,6 +246,8 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       const uint32_t s_tmem = tmem_base + (2 * t + u) * BQRY + lane_addr;
+      // 32-query chunks that hold at least one query (M = 16 new tokens: one chunk instead of four)
+      const int n_chunks = min(BQRY / 32, (p.M - q0 + 31) / 32);
       // causal: this key is visible to query q0 + col iff col >= key - P - q0
       const int cmin = p.causal ? (key - p.P - q0) : 0;
       const bool masked = p.causal && (tile[t].k0 + BKEY - 1 - p.P > q0);
@@ -257,7 +259,7 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const float c_g = -0.6931471805599453f * p.pert_log2;
         const uint32_t* hrow = my_hash + u * 128;
 #pragma unroll 1
-        for (int c = 0; c < BQRY / 32; ++c) {
+        for (int c = 0; c < n_chunks; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
 #pragma unroll
@@ -278,7 +280,7 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
       } else if (PERT || masked) {
-        for (int c = 0; c < BQRY / 32; ++c) {
+        for (int c = 0; c < n_chunks; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
 #pragma unroll
@@ -300,7 +302,7 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BQRY / 32; ++c) {
+        for (int c = 0; c < n_chunks; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
 #pragma unroll
@@ -345,6 +347,61 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem_base, kCsTmemCols);
   }
+}
+
+// Per-key statistics from scores kept in memory by the attention pass (small problems): thread = key,
+//   sum_p[key] = sum_i 2^(t[i][key] - lse[i]),  sum_p2 likewise with squares, i over the M queries in order.
+// No q, k, tensor cores or noise here: t already holds the (perturbed) scores in the log2 domain.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colstats_from_scores_kernel(const float* __restrict__ scores, long long pitch, const float* __restrict__ lse,
+                            void* __restrict__ sum_p, void* __restrict__ sum_p2, int M, int L, int first_query_off,
+                            int stats_fp32, const int* __restrict__ status) {
+  if (*reinterpret_cast<const volatile int*>(status) != 0) return;
+  const int key = blockIdx.x * blockDim.x + threadIdx.x;
+  const long long bh = blockIdx.y;
+  if (key >= L) return;
+  const float* t = scores + bh * M * pitch + key;
+  const float* l = lse + bh * M;
+  float a1 = 0.f, a2 = 0.f;
+  // causal: query i sees this key iff i >= key - P; the attention pass never wrote the scores of the others
+  int i = max(0, key - first_query_off);
+  for (; i + 4 <= M; i += 4) {           // four independent loads in flight
+    const float t0 = __ldg(t + (i + 0) * pitch), t1 = __ldg(t + (i + 1) * pitch);
+    const float t2 = __ldg(t + (i + 2) * pitch), t3 = __ldg(t + (i + 3) * pitch);
+    const float p0 = ex2_approx(t0 - __ldg(l + i)), p1 = ex2_approx(t1 - __ldg(l + i + 1));
+    const float p2 = ex2_approx(t2 - __ldg(l + i + 2)), p3 = ex2_approx(t3 - __ldg(l + i + 3));
+    a1 += p0; a2 = fmaf(p0, p0, a2);
+    a1 += p1; a2 = fmaf(p1, p1, a2);
+    a1 += p2; a2 = fmaf(p2, p2, a2);
+    a1 += p3; a2 = fmaf(p3, p3, a2);
+  }
+  for (; i < M; ++i) {
+    const float pr = ex2_approx(__ldg(t + i * pitch) - __ldg(l + i));
+    a1 += pr;
+    a2 = fmaf(pr, pr, a2);
+  }
+  const long long o = bh * L + key;
+  if (stats_fp32) {
+    static_cast<float*>(sum_p)[o] = a1;
+    if (sum_p2 != nullptr) static_cast<float*>(sum_p2)[o] = a2;
+  } else {
+    static_cast<T*>(sum_p)[o] = Io<T>::from_f(a1);
+    if (sum_p2 != nullptr) static_cast<T*>(sum_p2)[o] = Io<T>::from_f(a2);
+  }
+}
+
+template <typename T>
+int launch_from_scores(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds) {
+  const int L = a.P + a.M;
+  const long long bh = static_cast<long long>(a.B) * a.Hq;
+  if (bh > 65535) return TRN_E_SHAPE;
+  dim3 grid(static_cast<unsigned>((L + 255) / 256), static_cast<unsigned>(bh));
+  // non-causal: every query sees every key (offset = L makes key - offset negative for all keys)
+  colstats_from_scores_kernel<T><<<grid, 256, 0, st>>>(a.scores, a.score_pitch, a.lse, a.sum_p, a.sum_p2, a.M, L,
+                                                       a.causal ? a.P : L, a.stats_fp32, ds.status);
+  TRN_CUDA_TRY(cudaGetLastError());
+  return TRN_OK;
 }
 
 template <typename T, int D, bool PERT>
@@ -416,6 +473,13 @@ int launch_colstats(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState
   if (a.noise_mode != TRN_NOISE_NONE && !(a.tau > 0.f)) return TRN_E_SHAPE;
   if (a.noise_mode == TRN_NOISE_TENSOR && a.noise == nullptr) return TRN_E_NULL;
   if (a.lse == nullptr || a.sum_p == nullptr) return TRN_E_NULL;
+  if (a.scores != nullptr) {
+    // scores kept by the attention pass: no second q k^T
+    if (a.score_pitch < a.P + a.M) return TRN_E_SHAPE;
+    if (a.dtype == TRN_BF16) return launch_from_scores<__nv_bfloat16>(a, st, ds);
+    if (a.dtype == TRN_FP16) return launch_from_scores<__half>(a, st, ds);
+    return TRN_E_DTYPE;
+  }
   if (!ht_ok(a.q) || !ht_ok(a.k_cache)) return a.q.ptr == nullptr || a.k_cache.ptr == nullptr ? TRN_E_NULL : TRN_E_ALIGN;
   if (a.dtype == TRN_BF16) return launch_typed<__nv_bfloat16>(a, st, ds);
   if (a.dtype == TRN_FP16) return launch_typed<__half>(a, st, ds);

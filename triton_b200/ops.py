@@ -127,11 +127,14 @@ def _noise_fields(noise: Optional[torch.Tensor]):
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o: Optional[torch.Tensor], *,
               P: int, causal: bool, scale: float, lse: Optional[torch.Tensor] = None,
               noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
-              seed: int = 0, single_p: bool = False, workspace: Optional[torch.Tensor] = None) -> None:
+              seed: int = 0, single_p: bool = False, workspace: Optional[torch.Tensor] = None,
+              lse_pert: Optional[torch.Tensor] = None, scores: Optional[torch.Tensor] = None) -> None:
     """o = softmax(scale * q k^T [causal]) v over keys [0, P+M).  All tensors are (b, s, h, d) views.
     ``workspace`` (a uint8 CUDA tensor of attention_workspace_bytes(...) bytes) lets small launches
-    split the key range over more CTAs."""
-    _need_cuda(q, k_cache, v_cache, o, lse, noise, workspace)
+    split the key range over more CTAs.  With noise and ``lse_pert`` ([B, Hq, M] fp32) one pass gives o, lse
+    and the perturbed scores' lse; ``scores`` ([B, Hq, M, pitch] fp32, pitch a multiple of 32) receives every
+    score in the log2 domain for attn_colstats(scores=...)."""
+    _need_cuda(q, k_cache, v_cache, o, lse, noise, workspace, lse_pert, scores)
     B, M, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     if k_cache.shape[1] < P + M or v_cache.shape[1] < P + M:
@@ -141,6 +144,11 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o: 
                       B, M, P, Hq, Hkv, D, _dtype_code(q), int(causal), float(scale), noise_mode, float(tau),
                       nptr, nb, nh, ni, seed, int(single_p), _ptr(workspace),
                       0 if workspace is None else workspace.numel() * workspace.element_size())
+    a.lse_pert = _ptr(lse_pert)
+    if scores is not None:
+        if scores.dtype != torch.float32 or scores.dim() != 4 or not scores.is_contiguous():
+            raise ValueError("scores must be a contiguous float32 [B, Hq, M, pitch] tensor")
+        a.scores, a.score_pitch = scores.data_ptr(), scores.shape[3]
     L.check(L.load().trinity_attention(C.byref(a), _stream()))
 
 
@@ -154,15 +162,18 @@ def attention_workspace_bytes(B: int, M: int, P: int, Hq: int, Hkv: int, D: int)
 def attn_colstats(q: torch.Tensor, k_cache: torch.Tensor, lse: torch.Tensor, sum_p: torch.Tensor,
                   sum_p2: Optional[torch.Tensor] = None, *, P: int, causal: bool, scale: float,
                   noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
-                  seed: int = 0) -> None:
-    """Per-key sums over queries of the attention probabilities (and of their squares)."""
-    _need_cuda(q, k_cache, lse, sum_p, sum_p2, noise)
+                  seed: int = 0, scores: Optional[torch.Tensor] = None) -> None:
+    """Per-key sums over queries of the attention probabilities (and of their squares).  With ``scores`` (kept by
+    attention(scores=...)) they are summed from memory instead of recomputing q k^T."""
+    _need_cuda(q, k_cache, lse, sum_p, sum_p2, noise, scores)
     B, M, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     nptr, nb, nh, ni = _noise_fields(noise)
     a = L.TrnColStatsArgs(_head_tensor(q), _head_tensor(k_cache), lse.data_ptr(), sum_p.data_ptr(), _ptr(sum_p2),
                           B, M, P, Hq, Hkv, D, _dtype_code(q), int(sum_p.dtype == torch.float32), int(causal),
                           float(scale), noise_mode, float(tau), nptr, nb, nh, ni, seed)
+    if scores is not None:
+        a.scores, a.score_pitch = scores.data_ptr(), scores.shape[3]
     L.check(L.load().trinity_attn_colstats(C.byref(a), _stream()))
 
 
