@@ -43,6 +43,15 @@ WORKLOADS = {
     "rmsnorm_llama": dict(variant="rmsnorm", rows=16384, cols=4096),
     "rmsnorm_falcon": dict(variant="rmsnorm", rows=8192, cols=4544),
 }
+# The reference's own benchmark shapes (M = 16 new tokens, P = 1024 cached keys, fp16; vanilla_llama_benchmark.py
+# and its siblings), run the way its harness runs them: IR program -> convert_ir_to_triton -> forward(*tensors),
+# 10 warm-up calls, CUDA-graph capture, 100 replays.  `--impl reference` runs the Triton module the reference's own
+# generator emitted for the same program (oracle/_ref/, produced by oracle/make_reference_kernels.py) through the
+# same procedure on the same GPU.
+NATIVE_PROGRAMS = ("vanilla", "prenorm", "prenorm_fused", "qknorm", "keyformer", "roco", "rmsnorm")
+for _prog in NATIVE_PROGRAMS:
+    for _model in ("llama", "falcon"):
+        WORKLOADS[f"native_{_prog}_{_model}"] = dict(variant="native", program=_prog, model=_model)
 METRIC = "fused attn-block TFLOP/s"
 
 
@@ -440,6 +449,66 @@ def run_rmsnorm(args, w):
     print(json.dumps(line))
 
 
+def run_native(args, w):
+    """One of the reference's own shapes through the reference's own harness procedure; ours or the reference's
+    generated Triton kernels."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import importlib.util
+    import torch
+    from triton_b200 import _lib as L
+    from triton_b200.convert_module import convert_ir_to_triton
+    from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT, AttnBlockBenchmark
+    prog, model = w["program"], w["model"]
+    consts = MODEL_CONFIGS[model]
+    M, N, D, H, P = (consts[k] for k in ("M", "N", "D", "H", "P"))
+    ref_path = os.path.join(ROOT, "oracle", "_ref", f"{prog}_{model}.py")
+    base = {"metric": METRIC, "unit": "TFLOP/s", "n_gpus": 1, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "program": prog, "model": model, **consts,
+                       "procedure": "10 warm-up calls, CUDA-graph capture, 100 replays (the reference harness)"}}
+    if args.impl == "reference" and not os.path.isfile(ref_path):
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref is not generated on this machine "
+                          "(python oracle/make_reference_kernels.py needs the reference checkout)"}))
+        return
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    bench = AttnBlockBenchmark(consts, seed=42)
+    if args.impl == "reference":
+        spec = importlib.util.spec_from_file_location(f"refgen_{prog}_{model}", ref_path)
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[spec.name] = mod
+        spec.loader.exec_module(mod)
+    else:
+        ir = open(os.path.join(ROOT, "triton_b200", "ir_programs", f"{prog}.txt")).read()
+        mod = bench.compile_and_load_kernel(convert_ir_to_triton(ir, SHAPE_DICT, consts), 0)
+    bench.create_test_tensors(mod.TENSOR_PARAMS)
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    try:
+        ms = bench.benchmark_kernel(mod, warmup_runs=10, benchmark_runs=100)
+        err = None
+    except Exception as e:                       # the reference's QKNorm kernels overflow fp16 at these inputs
+        ms, err = float("nan"), str(e)
+    clocks = sampler.stop()
+    if prog == "rmsnorm":
+        flops = 3 * M * N
+    else:
+        flops = 2 * M * N * 3 * H * D + 4 * H * D * M * (P + M)
+    line = dict(base, value=None if err else flops / (ms * 1e-3) / 1e12, steps=100, warmup=10,
+                ms_per_step=None if err else ms, us_per_call=None if err else ms * 1e3, clocks=clocks,
+                gpu_launches=100, e2e=None)
+    if err:
+        line["error"] = err
+    if args.impl == "reference":
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                                "sample": "the Triton module the reference generator emits for this program, on this GPU"}
+    elif L.kernel_status() != 0:
+        raise RuntimeError("kernel status")
+    print(json.dumps(line))
+    bench.cleanup()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -450,7 +519,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if w["variant"] == "rmsnorm":
+    if w["variant"] == "native":
+        run_native(args, w)
+    elif w["variant"] == "rmsnorm":
         run_rmsnorm(args, w)
     elif args.impl == "reference":
         run_reference(args, w)
