@@ -88,7 +88,16 @@ struct TileInfo {
   bool present;   // the tile exists (it has query rows)
 };
 
-template <typename T, int D, int MODE, bool SPLIT>
+// DUP (at most 32 queries per head: decode, chunked prefill, the reference's M = 16): the queries are loaded
+// four times into the 128 tile rows, so that S has four identical 32-row replicas, and replica r (= warp r of
+// the tile's softmax warpgroup) works only on score columns [32 r, 32 r + 32) of every key block.  Its rows of P
+// are zero elsewhere, so each replica accumulates an independent partial (o, lse) over a quarter of the keys;
+// the four are merged inside the CTA through shared memory before anything is written.  The per-row work of
+// a thread drops four-fold.
+constexpr int kDupRows = 32;
+constexpr int kDup = BQ / kDupRows;
+
+template <typename T, int D, int MODE, bool SPLIT, bool DUP>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
@@ -216,8 +225,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int t = 0; t < 2; ++t) {
         if (tile[t].n_blocks) {
 #pragma unroll
-          for (int c = 0; c < SM::kChunks; ++c)
-            tma_load_head_tile(q_s(t) + c * SM::kChunkBytes, &tm_q, q_full, p.qi, c * 64, tile[t].q0, tile[t].h, b);
+          for (int c = 0; c < SM::kChunks; ++c) {
+            if constexpr (DUP) {
+              // the descriptor's box is 32 rows: the same queries land in each quarter of the tile
+#pragma unroll
+              for (int rep = 0; rep < kDup; ++rep)
+                tma_load_head_tile(q_s(t) + c * SM::kChunkBytes + rep * kDupRows * 128, &tm_q, q_full, p.qi, c * 64,
+                                   tile[t].q0, tile[t].h, b);
+            } else {
+              tma_load_head_tile(q_s(t) + c * SM::kChunkBytes, &tm_q, q_full, p.qi, c * 64, tile[t].q0, tile[t].h, b);
+            }
+          }
         }
       }
     }
@@ -338,13 +356,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int t = (warp - 2) >> 2;                 // which tile this warpgroup owns
     const int quad = warp & 3;                     // TMEM lane quarter of this warp
     const int row = quad * 32 + lane;
-    const int q_abs = tile[t].q0 + row;
+    const int q_abs = tile[t].q0 + (DUP ? (row & (kDupRows - 1)) : row);
     const int h = tile[t].h;
     const int n_blocks = tile[t].n_blocks;
     const bool row_valid = q_abs < p.M;
     // a warp whose 32 rows all lie past the last query (M = 16 new tokens fill half of one warp) only keeps
     // the barrier protocol going: its rows of S / P / O are never stored and feed no other row
-    const bool warp_active = tile[t].q0 + quad * 32 < p.M;
+    const bool warp_active = DUP || tile[t].q0 + quad * 32 < p.M;
+    auto my_chunk = [&](int c) { return !DUP || c == quad; };      // DUP: replica `quad` owns chunk `quad`
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int limit = p.causal ? min(p.P + q_abs, p.L - 1) : p.L - 1;               // last visible key of this row
     const int limit_min = p.causal ? min(p.P + tile[t].q0, p.L - 1) : p.L - 1;     // ... of the tile's first row
@@ -465,6 +484,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // one pass, chunk-wise online log-sum-exp of the perturbed scores
 #pragma unroll 1
         for (int c = 0; c < BKV / 32; ++c) {
+          if (!my_chunk(c)) continue;
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
           pert_chunk(kv0, c, masked);
@@ -481,6 +501,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // when the projection's weights have just swept the L2 (the reference's M = 16 shapes)
 #pragma unroll 1
         for (int c = 0; c < BKV / 32; ++c) {
+          if (!my_chunk(c)) continue;
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
           if (masked) {
@@ -502,6 +523,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       } else if (masked) {
         for (int c = 0; c < BKV / 32; ++c) {
+          if (!my_chunk(c)) continue;
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
 #pragma unroll
@@ -510,6 +532,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       } else {
         for (int c = 0; c < BKV / 32; ++c) {
+          if (!my_chunk(c)) continue;
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
           float m0 = fmaxf(__uint_as_float(r[0]), __uint_as_float(r[1]));
@@ -557,9 +580,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll 1
         for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t pk[SPLIT ? 32 : 16];
+          if (my_chunk(c)) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
-          uint32_t pk[SPLIT ? 32 : 16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, neg_m2);
@@ -576,6 +600,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               const float2 lo = __ffma2_rn(Io<T>::unpack2(hi), minus1, pp);    // p - hi, exact
               pk[16 + (i >> 1)] = Io<T>::pack2(lo.x, lo.y);
             }
+          }
+          } else {
+            // another replica's columns: this replica's p is zero there
+#pragma unroll
+            for (int i = 0; i < (SPLIT ? 32 : 16); ++i) pk[i] = 0u;
           }
           if constexpr (SPLIT) {
             tmem_st32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(pk));
@@ -601,6 +630,105 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const long long part_row =
         ((static_cast<long long>(split) * p.B + b) * p.Hq + h) * p.M + q_abs;   // row of the partial results
     if (MODE == 1) { m_run = m2_run; l_run = l2_run; }        // MODE 1 reports the perturbed value as its lse
+    if constexpr (DUP) {
+      // ---- merge the four replicas of this tile inside the CTA.  The k / v stages and the q tiles are free once
+      //      the last MMAs of BOTH tiles have run (they share the k / v stream): o goes through the stage area as
+      //      [replica][column][row] fp32 (conflict-free both ways), the log-sum-exps through the tile's q area.
+      if (tile[t].present && n_blocks > 0) {          // uniform over the warpgroup
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (ok && tile[u].n_blocks > 0) {
+            ok = kHasPV ? mbar_wait(pv_done(u), (tile[u].n_blocks - 1) & 1, ctl, KST_TIMEOUT_CONSUMER)
+                        : mbar_wait(s_full(u), (tile[u].n_blocks - 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
+            ok = __all_sync(0xffffffffu, ok);
+          }
+        }
+        float* xo = reinterpret_cast<float*>(smem_gen + SM::kKVOff) + t * (kDup * D * kDupRows);
+        float* xl = reinterpret_cast<float*>(smem_gen + SM::kQOff + t * SM::kTileBytes);     // [2][replica][row]
+        const float lse1 = m_run + log2f(l_run);            // -inf when this replica saw no visible key
+        const float lse2v = (MODE == 2) ? m2_run + log2f(l2_run) : 0.f;
+        if (ok && kHasPV) {
+          tc_fence_after();
+          const float inv_l = (l_run > 0.f) ? 1.0f / l_run : 0.f;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            tmem_ld32(o_tmem + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) xo[(quad * D + c * 32 + i) * kDupRows + lane] = __uint_as_float(r[i]) * inv_l;
+          }
+          tc_fence_before();
+        }
+        xl[quad * kDupRows + lane] = lse1;
+        if (MODE == 2) xl[(kDup + quad) * kDupRows + lane] = lse2v;
+        // every warp of the warpgroup gets here (all waits above are bounded): named barrier 1 + t, 128 threads
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
+        // weights of the four replicas for row `lane`
+        float w[kDup], mx = -INFINITY, tot = 0.f;
+#pragma unroll
+        for (int rp = 0; rp < kDup; ++rp) { w[rp] = xl[rp * kDupRows + lane]; mx = fmaxf(mx, w[rp]); }
+#pragma unroll
+        for (int rp = 0; rp < kDup; ++rp) { w[rp] = (w[rp] == -INFINITY) ? 0.f : ex2_approx(w[rp] - mx); tot += w[rp]; }
+        const float inv_tot = 1.0f / tot;
+        const int qrow = tile[t].q0 + lane;                 // this warp writes columns [quad * D/4, (quad+1) * D/4) of row `lane`
+        const bool out_valid = qrow < p.M;
+        const long long prow_idx = ((static_cast<long long>(split) * p.B + b) * p.Hq + h) * p.M + qrow;
+        if (ok && kHasPV && out_valid) {
+          constexpr int CW = D / kDup;                      // columns per warp: 32 or 16
+          float acc[CW];
+#pragma unroll
+          for (int i = 0; i < CW; ++i) {
+            float v = 0.f;
+#pragma unroll
+            for (int rp = 0; rp < kDup; ++rp) v = fmaf(w[rp], xo[(rp * D + quad * CW + i) * kDupRows + lane], v);
+            acc[i] = v * inv_tot;
+          }
+          if (split_out) {
+            float* dst = p.part_o + prow_idx * D + quad * CW;
+#pragma unroll
+            for (int i = 0; i < CW; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+          } else {
+            T* dst = static_cast<T*>(p.o) + static_cast<long long>(b) * p.o_sb + static_cast<long long>(qrow) * p.o_ss +
+                     static_cast<long long>(h) * p.o_sh + quad * CW;
+#pragma unroll
+            for (int i = 0; i < CW; i += 8) {
+              uint4 v;
+              v.x = Io<T>::pack2(acc[i], acc[i + 1]); v.y = Io<T>::pack2(acc[i + 2], acc[i + 3]);
+              v.z = Io<T>::pack2(acc[i + 4], acc[i + 5]); v.w = Io<T>::pack2(acc[i + 6], acc[i + 7]);
+              *reinterpret_cast<uint4*>(dst + i) = v;
+            }
+          }
+        }
+        if (ok && out_valid && quad == 0) {
+          const float lse_m = mx + log2f(tot);
+          float lse2_m = 0.f;
+          if (MODE == 2) {
+            float m2 = -INFINITY, t2 = 0.f;
+#pragma unroll
+            for (int rp = 0; rp < kDup; ++rp) m2 = fmaxf(m2, xl[(kDup + rp) * kDupRows + lane]);
+#pragma unroll
+            for (int rp = 0; rp < kDup; ++rp) {
+              const float v = xl[(kDup + rp) * kDupRows + lane];
+              if (v != -INFINITY) t2 += ex2_approx(v - m2);
+            }
+            lse2_m = m2 + log2f(t2);
+          }
+          const long long li = (static_cast<long long>(b) * p.Hq + h) * p.M + qrow;
+          if (split_out) {
+            p.part_lse[prow_idx] = lse_m;
+            if (MODE == 2) p.part_lse2[prow_idx] = lse2_m;
+          } else {
+            if (p.lse != nullptr) p.lse[li] = lse_m;
+            if (MODE == 2) p.lse_pert[li] = lse2_m;
+          }
+        }
+      } else if (split_out && tile[t].present && quad == 0 && tile[t].q0 + lane < p.M) {
+        // this CTA's key range misses the tile: weight 0 in the merge kernel
+        const long long prow_idx = ((static_cast<long long>(split) * p.B + b) * p.Hq + h) * p.M + tile[t].q0 + lane;
+        p.part_lse[prow_idx] = -INFINITY;
+        if (MODE == 2) p.part_lse2[prow_idx] = -INFINITY;
+      }
+    } else {
     if (ok && kHasPV && n_blocks > 0 && warp_active) {
       ok = mbar_wait(pv_done(t), (n_blocks - 1) & 1, ctl, KST_TIMEOUT_CONSUMER);
       ok = __all_sync(0xffffffffu, ok);
@@ -646,6 +774,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (p.lse != nullptr) p.lse[li] = m_run + log2f(l_run);
       if (MODE == 2) p.lse_pert[li] = m2_run + log2f(l2_run);
     }
+    }   // !DUP
   }
 
   // ------------------------------- teardown -------------------------------
@@ -735,13 +864,13 @@ size_t split_bytes(int n_splits, long long rows, int D, bool with_o) {
   return o_b + 2 * split_lse_bytes(n_splits, rows);
 }
 
-template <typename T, int D, int MODE, bool SPLIT>
+template <typename T, int D, int MODE, bool SPLIT, bool DUP>
 int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   using SM = AttnSmem<D>;
   AttnParams p{};
   const int L = a.P + a.M;
   CUtensorMap tm_q, tm_k, tm_v;
-  int rc = make_head_tmap(&tm_q, &p.qi, a.q, a.M, a.Hq, a.B, D, BQ);
+  int rc = make_head_tmap(&tm_q, &p.qi, a.q, a.M, a.Hq, a.B, D, DUP ? kDupRows : BQ);
   if (rc != TRN_OK) return rc;
   rc = make_head_tmap(&tm_k, &p.ki, a.k_cache, L, a.Hkv, a.B, D, BKV);
   if (rc != TRN_OK) return rc;
@@ -783,7 +912,7 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
                        ? 1
                        : 0;
   p.status = ds.status;
-  auto kern = attn_fwd_kernel<T, D, MODE, SPLIT>;
+  auto kern = attn_fwd_kernel<T, D, MODE, SPLIT, DUP>;
   rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
   if (rc != TRN_OK) return rc;
   const long long ctas = rows_of_ctas * p.units;
@@ -795,28 +924,39 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   int n_splits = tls_attn_split_override > 0 ? tls_attn_split_override
                                              : attn_split_count(static_cast<int>(ctas), l_eff, ds.sm_count);
   if (n_splits > (L + BKV - 1) / BKV) n_splits = 1;
-  if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0) n_splits = 1;
+  const bool ws_ok = a.workspace != nullptr && (reinterpret_cast<uintptr_t>(a.workspace) & 255u) == 0;
+  if (!ws_ok) n_splits = 1;
   while (n_splits > 1 && split_bytes(n_splits, rows, D, MODE != 1) > a.workspace_bytes) --n_splits;
   p.n_splits = n_splits;
   p.ctas_per_split = static_cast<int>(ctas);
-  if (n_splits > 1) {
+  const int n_parts = n_splits;
+  if (n_parts > 1) {
     uint8_t* ws = static_cast<uint8_t*>(a.workspace);
-    const size_t l_b = split_lse_bytes(n_splits, rows);
+    const size_t l_b = split_lse_bytes(n_parts, rows);
     p.part_lse = reinterpret_cast<float*>(ws);
     p.part_lse2 = reinterpret_cast<float*>(ws + l_b);
     p.part_o = (MODE != 1) ? reinterpret_cast<float*>(ws + 2 * l_b) : nullptr;
   }
   kern<<<static_cast<int>(ctas * n_splits), kAttnThreads, SM::kTotal, st>>>(tm_q, tm_k, tm_v, p);
   TRN_CUDA_TRY(cudaGetLastError());
-  if (n_splits > 1) {
+  if (n_parts > 1) {
     const int warps_per_cta = 8;
     const long long cgrid = (rows + warps_per_cta - 1) / warps_per_cta;
     attn_combine_kernel<T, D><<<static_cast<int>(cgrid), warps_per_cta * 32, 0, st>>>(
         p.part_o, p.part_lse, static_cast<T*>(a.o.ptr), a.o.stride_b, a.o.stride_s, a.o.stride_h, a.lse,
-        MODE == 2 ? p.part_lse2 : nullptr, a.lse_pert, n_splits, a.B, a.Hq, a.M, ds.status);
+        MODE == 2 ? p.part_lse2 : nullptr, a.lse_pert, n_parts, a.B, a.Hq, a.M, ds.status);
     TRN_CUDA_TRY(cudaGetLastError());
   }
   return TRN_OK;
+}
+
+// few queries per head: the row-replicated variant
+template <typename T, int D, int MODE, bool SPLIT>
+int launch_variant(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
+  if constexpr (SPLIT || MODE == 1) {
+    if (a.M <= kDupRows) return launch_inst<T, D, MODE, SPLIT, true>(a, st, ds);
+  }
+  return launch_inst<T, D, MODE, SPLIT, false>(a, st, ds);
 }
 
 template <typename T>
@@ -824,18 +964,18 @@ int launch_typed(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   const bool pert = a.noise_mode != TRN_NOISE_NONE;
   const bool fused = pert && a.lse_pert != nullptr;     // attention and the perturbed log-sum-exp in one pass
   if (a.D == 128) {
-    if (fused) return a.single_p ? launch_inst<T, 128, 2, false>(a, st, ds) : launch_inst<T, 128, 2, true>(a, st, ds);
-    if (pert) return launch_inst<T, 128, 1, false>(a, st, ds);
+    if (fused) return a.single_p ? launch_variant<T, 128, 2, false>(a, st, ds) : launch_variant<T, 128, 2, true>(a, st, ds);
+    if (pert) return launch_variant<T, 128, 1, false>(a, st, ds);
     if (a.scores != nullptr)
-      return a.single_p ? launch_inst<T, 128, 3, false>(a, st, ds) : launch_inst<T, 128, 3, true>(a, st, ds);
-    return a.single_p ? launch_inst<T, 128, 0, false>(a, st, ds) : launch_inst<T, 128, 0, true>(a, st, ds);
+      return a.single_p ? launch_variant<T, 128, 3, false>(a, st, ds) : launch_variant<T, 128, 3, true>(a, st, ds);
+    return a.single_p ? launch_variant<T, 128, 0, false>(a, st, ds) : launch_variant<T, 128, 0, true>(a, st, ds);
   }
   if (a.D == 64) {
-    if (fused) return a.single_p ? launch_inst<T, 64, 2, false>(a, st, ds) : launch_inst<T, 64, 2, true>(a, st, ds);
-    if (pert) return launch_inst<T, 64, 1, false>(a, st, ds);
+    if (fused) return a.single_p ? launch_variant<T, 64, 2, false>(a, st, ds) : launch_variant<T, 64, 2, true>(a, st, ds);
+    if (pert) return launch_variant<T, 64, 1, false>(a, st, ds);
     if (a.scores != nullptr)
-      return a.single_p ? launch_inst<T, 64, 3, false>(a, st, ds) : launch_inst<T, 64, 3, true>(a, st, ds);
-    return a.single_p ? launch_inst<T, 64, 0, false>(a, st, ds) : launch_inst<T, 64, 0, true>(a, st, ds);
+      return a.single_p ? launch_variant<T, 64, 3, false>(a, st, ds) : launch_variant<T, 64, 3, true>(a, st, ds);
+    return a.single_p ? launch_variant<T, 64, 0, false>(a, st, ds) : launch_variant<T, 64, 0, true>(a, st, ds);
   }
   return TRN_E_SHAPE;
 }
