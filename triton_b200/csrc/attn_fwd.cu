@@ -381,6 +381,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     float* score_row = (p.scores != nullptr && row_valid)
                            ? p.scores + ((static_cast<long long>(b) * p.Hq + h) * p.M + q_abs) * p.score_pitch
                            : nullptr;
+    // DUP + noise tensor: the 32 noise values of the replica's chunk are requested before the wait for S, so that
+    // their latency (HBM, when the projection's weights have just swept the L2) overlaps that wait
+    uint4 noise_pre[4];
+    bool noise_pre_ok = false;
     // Perturbed scores of chunk c of block kv0 (S values in r[]): online log-sum-exp update, optional write-out.
     // t = (s * scale + g) * log2(e) / tau; with generated noise g = -ln2 * log2(E):  t = s * c_s + log2(E) * c_g
     auto pert_chunk = [&](int kv0, int c, bool masked) {
@@ -410,7 +414,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         static_cast<long long>(row_valid ? q_abs : 0) * p.noise.si + kv0 + c * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
-          const uint4 nv = __ldg(reinterpret_cast<const uint4*>(nrow + i));
+          const uint4 nv = (DUP && noise_pre_ok) ? noise_pre[i >> 3] : __ldg(reinterpret_cast<const uint4*>(nrow + i));
           const uint32_t w4[4] = {nv.x, nv.y, nv.z, nv.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -469,6 +473,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     for (int j = 0; j < n_blocks; ++j) {
       const int kv0 = (j0 + j) * BKV;
+      if constexpr (DUP && kPert) {
+        noise_pre_ok = p.noise.mode == TRN_NOISE_TENSOR && p.noise_vec_ok && (kv0 + BKV - 1) <= limit_min;
+        if (noise_pre_ok) {
+          const T* nrow = static_cast<const T*>(p.noise.ptr) + b * p.noise.sb + h * p.noise.sh +
+                          static_cast<long long>(row_valid ? q_abs : 0) * p.noise.si + kv0 + quad * 32;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) noise_pre[i] = __ldg(reinterpret_cast<const uint4*>(nrow + 8 * i));
+        }
+      }
       ok = mbar_wait(s_full(t), j & 1, ctl, KST_TIMEOUT_CONSUMER);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -558,7 +571,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         m_run = m_target;
       }
       // S_t(j) was produced after P_t(j-1) v (MMAs run in issue order), so O_t is quiescent here
+      bool r_holds_s = DUP;          // DUP: r[] still holds the replica's chunk of S from pass 1 ...
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        r_holds_s = false;           // ... unless it is used as scratch here
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           tmem_ld32(o_tmem + c * 32, r);
@@ -582,8 +597,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int c = 0; c < BKV / 32; ++c) {
           uint32_t pk[SPLIT ? 32 : 16];
           if (my_chunk(c)) {
-          tmem_ld32(s_tmem + c * 32, r);
-          tmem_wait_ld();
+          if (!r_holds_s) {          // warp-uniform
+            tmem_ld32(s_tmem + c * 32, r);
+            tmem_wait_ld();
+          }
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, neg_m2);
