@@ -597,27 +597,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int c = 0; c < BKV / 32; ++c) {
           uint32_t pk[SPLIT ? 32 : 16];
           if (my_chunk(c)) {
-          if (!r_holds_s) {          // warp-uniform
-            tmem_ld32(s_tmem + c * 32, r);
-            tmem_wait_ld();
-          }
+            if (!r_holds_s) {          // warp-uniform
+              tmem_ld32(s_tmem + c * 32, r);
+              tmem_wait_ld();
+            }
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, neg_m2);
-            float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-            if constexpr (kMasked) {
-              if (kv0 + c * 32 + i > limit) pp.x = 0.f;
-              if (kv0 + c * 32 + i + 1 > limit) pp.y = 0.f;
+            for (int i = 0; i < 32; i += 2) {
+              const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, neg_m2);
+              float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+              if constexpr (kMasked) {
+                if (kv0 + c * 32 + i > limit) pp.x = 0.f;
+                if (kv0 + c * 32 + i + 1 > limit) pp.y = 0.f;
+              }
+              lsum = __fadd2_rn(lsum, pp);
+              const uint32_t hi = Io<T>::pack2(pp.x, pp.y);
+              pk[i >> 1] = hi;
+              if constexpr (SPLIT) {
+                // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
+                const float2 lo = __ffma2_rn(Io<T>::unpack2(hi), minus1, pp);    // p - hi, exact
+                pk[16 + (i >> 1)] = Io<T>::pack2(lo.x, lo.y);
+              }
             }
-            lsum = __fadd2_rn(lsum, pp);
-            const uint32_t hi = Io<T>::pack2(pp.x, pp.y);
-            pk[i >> 1] = hi;
-            if constexpr (SPLIT) {
-              // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
-              const float2 lo = __ffma2_rn(Io<T>::unpack2(hi), minus1, pp);    // p - hi, exact
-              pk[16 + (i >> 1)] = Io<T>::pack2(lo.x, lo.y);
-            }
-          }
           } else {
             // another replica's columns: this replica's p is zero there
 #pragma unroll
