@@ -87,3 +87,36 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     monkeypatch.setattr(L, "LIB_PATH", tmp_path / "libtrinity_b200.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         L.load()
+
+
+def test_workspace_sizing_policies(lib):
+    """Host-side sizing (no GPU needed): which shapes ask for split-KV partials and which keep their scores."""
+    def attn_ws(B, M, P, Hq, Hkv, D):
+        a = L.TrnAttnArgs()
+        a.B, a.M, a.P, a.Hq, a.Hkv, a.D = B, M, P, Hq, Hkv, D
+        return lib.trinity_attention_workspace(C.byref(a))
+
+    def align(v):
+        return (v + 255) // 256 * 256
+
+    # the reference's Llama shape: 32 CTAs -> 4 key splits; two lse arrays and one o array of fp32 partials
+    rows = 1 * 32 * 16
+    assert attn_ws(1, 16, 1024, 32, 32, 128) == 2 * align(4 * rows * 4) + align(4 * rows * 128 * 4)
+    assert attn_ws(8, 2048, 0, 32, 8, 128) == 0            # fills the GPU many times over
+    assert attn_ws(1, 16, 128, 4, 4, 128) == 0             # two key blocks: nothing to split
+    assert attn_ws(1, 16, 1024, 32, 32, 96) == 0           # unsupported head_dim: no claim
+
+    def block_ws(variant, B, M, P, Hq, Hkv, D, N=4096):
+        a = L.TrnBlockArgs()
+        a.variant, a.B, a.M, a.P, a.N, a.Hq, a.Hkv, a.D = L.VARIANTS[variant], B, M, P, N, Hq, Hkv, D
+        return lib.trinity_attn_block_workspace(C.byref(a))
+
+    base = align(16 * 4) + 2 * align(rows * 4)
+    split = attn_ws(1, 16, 1024, 32, 32, 128)
+    scores = align(rows * 1056 * 4)                        # [B, Hq, M, pitch] fp32, pitch = 1040 rounded up to 32
+    assert block_ws("vanilla", 1, 16, 1024, 32, 32, 128) == base + split
+    assert block_ws("keyformer", 1, 16, 1024, 32, 32, 128) == base + split + scores
+    assert block_ws("roco", 1, 16, 1024, 32, 32, 128) == base + split + scores
+    # large statistics problems recompute q k^T instead of keeping 4 GiB of scores
+    big = block_ws("keyformer", 4, 4096, 0, 32, 8, 128)
+    assert big == align(4 * 4096 * 4) + 2 * align(4 * 32 * 4096 * 4)
