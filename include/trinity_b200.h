@@ -224,8 +224,11 @@ int trinity_convert(const void* src, void* dst, int64_t n, int dtype16, int to_f
  * Whole block, the unit the reference's generated forward() computes (TritonGen.py:590-708):
  *   [PreNorm row statistics] -> QKV projection (+QKNorm, +cache append) -> attention ->
  *   [KeyFormer / RoCo per-key statistics].
- * `workspace` holds fp32 row scales [B*M], lse [B,Hq,M] and perturbed lse [B,Hq,M];
- * trinity_attn_block_workspace() returns the bytes needed (256-byte aligned base required).
+ * `workspace` (256-byte aligned base) holds, required: fp32 row scales [B*M], lse [B,Hq,M] and perturbed lse
+ * [B,Hq,M]; optional, used when the caller lent them: the split-KV partials of the attention launch (shapes that
+ * would fill less than half of the SMs) and, for KeyFormer / RoCo problems whose [B,Hq,M,P+M] fp32 scores fit in
+ * 32 MiB, those scores (the statistics are then summed from memory instead of a second q k^T pass).
+ * trinity_attn_block_workspace() returns required + optional; any size from the required part upwards is accepted.
  * skip_projection != 0: q / k_cache / v_cache are taken as given (BASELINE configs 4 and 5).
  * ---------------------------------------------------------------------------------------------- */
 typedef struct {
