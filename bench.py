@@ -52,6 +52,9 @@ NATIVE_PROGRAMS = ("vanilla", "prenorm", "prenorm_fused", "qknorm", "keyformer",
 for _prog in NATIVE_PROGRAMS:
     for _model in ("llama", "falcon"):
         WORKLOADS[f"native_{_prog}_{_model}"] = dict(variant="native", program=_prog, model=_model)
+# ... and the neighbouring LoRA operator on the configurations of lora_benchmark.py:545-548
+for _cfg in ("base", "large"):
+    WORKLOADS[f"native_lora_{_cfg}"] = dict(variant="native", program="lora", model=_cfg)
 METRIC = "fused attn-block TFLOP/s"
 
 
@@ -459,10 +462,11 @@ def run_native(args, w):
     import torch
     from triton_b200 import _lib as L
     from triton_b200.convert_module import convert_ir_to_triton
-    from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT, AttnBlockBenchmark
+    from triton_b200.harness import AttnBlockBenchmark, tables_for
     prog, model = w["program"], w["model"]
-    consts = MODEL_CONFIGS[model]
-    M, N, D, H, P = (consts[k] for k in ("M", "N", "D", "H", "P"))
+    SHAPE_DICT, consts = tables_for(prog, model)
+    M, N, P = (consts[k] for k in ("M", "N", "P"))
+    D, H = consts.get("D"), consts.get("H")
     ref_path = os.path.join(ROOT, "oracle", "_ref", f"{prog}_{model}.py")
     base = {"metric": METRIC, "unit": "TFLOP/s", "n_gpus": 1, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
@@ -473,7 +477,7 @@ def run_native(args, w):
                           "(python oracle/make_reference_kernels.py needs the reference checkout)"}))
         return
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-    bench = AttnBlockBenchmark(consts, seed=42)
+    bench = AttnBlockBenchmark(consts, seed=42, shape_dict=SHAPE_DICT)
     if args.impl == "reference":
         spec = importlib.util.spec_from_file_location(f"refgen_{prog}_{model}", ref_path)
         mod = importlib.util.module_from_spec(spec)
@@ -493,6 +497,9 @@ def run_native(args, w):
     clocks = sampler.stop()
     if prog == "rmsnorm":
         flops = 3 * M * N
+    elif prog == "lora":
+        R = consts["R"]
+        flops = 2 * M * N * P + 2 * M * N * R + 2 * M * R * P
     else:
         flops = 2 * M * N * 3 * H * D + 4 * H * D * M * (P + M)
     line = dict(base, value=None if err else flops / (ms * 1e-3) / 1e12, steps=100, warmup=10,

@@ -121,6 +121,25 @@ typedef struct {
 int trinity_qkv_project(const TrnProjArgs* a, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * LoRA linear layer, the neighbouring operator of the reference's lora_benchmark.py (tensor table :41-64;
+ * arithmetic as its generator spells it, TritonGen.py:3092-3094):
+ *   d = x @ a            [M, R]   (kept as a 16-bit tensor between the two steps, like the reference's D)
+ *   o = x @ w + d @ b    [M, P]   (both products accumulated in fp32 in one accumulator)
+ * x [M, N], w [N, P], a [N, R], b [R, P], all row-major and contiguous; N % 8 == 0, P % 64 == 0, R % 64 == 0.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  const void* w;
+  const void* a;
+  const void* b;
+  void* o;
+  void* d;      /* [M, R] scratch / output of the first step */
+  int M, N, P, R;
+  int dtype;
+} TrnLoraArgs;
+int trinity_lora(const TrnLoraArgs* a, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Attention core (ref_rms.py:72-81): for every (b, query head h) with kv head h / (Hq/Hkv)
  *   s = scale * q k^T over keys [0, P+M);  causal: query i sees keys j <= P + i
  *   o = softmax(s) v;  lse (optional) = log-sum-exp of s in base 2:  log2(sum_j 2^(s_ij*log2 e))

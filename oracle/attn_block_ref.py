@@ -251,3 +251,15 @@ def attn_block_chunked(variant: str, *, head_chunk: int = 4, **kw) -> Dict[str, 
     if sp2:
         res["sum_p2"] = torch.cat(sp2, dim=0)
     return res
+
+
+def lora(X: torch.Tensor, W: torch.Tensor, A: torch.Tensor, B: torch.Tensor,
+         round_d: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
+    """LoRA linear layer in fp32: D = X @ A, O = X @ W + D @ B (tensor table lora_benchmark.py:41-64; the arithmetic
+    as the reference generator spells it, TritonGen.py:3092-3094).  round_d: D is kept as a 16-bit tensor between the
+    two steps by the operator surface (and by the reference's kernels); rounding it here gives the like-for-like value."""
+    Xf, Wf, Af, Bf = X.float(), W.float(), A.float(), B.float()
+    D = Xf @ Af
+    if round_d is not None:
+        D = D.to(round_d).float()
+    return {"D": D, "O": Xf @ Wf + D @ Bf}

@@ -5,7 +5,7 @@ the native_* workloads).
 
     python oracle/make_reference_kernels.py [/path/to/reference]
 
-Writes oracle/_ref/<program>_<model>.py for model in {llama, falcon} (git-ignored: derived from the reference,
+Writes oracle/_ref/<program>_<model>.py for model in {llama, falcon} (the LoRA program: its configurations {base, large}) (git-ignored: derived from the reference,
 regenerated wherever the reference checkout is present, never committed).  The IR text is this repository's
 (`triton_b200/ir_programs/`; the reference ships no IR files) with one substitution: the head tile of the
 parallel loops, written symbolically there (`(ploop 0 N D n`), is given as the number the model uses
@@ -21,7 +21,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 sys.path.insert(0, ROOT)
 
-from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT  # noqa: E402
+from triton_b200.harness import LORA_CONFIGS, MODEL_CONFIGS, tables_for  # noqa: E402
 
 
 def generate(ref_dir: str, out_dir: str) -> int:
@@ -31,14 +31,18 @@ def generate(ref_dir: str, out_dir: str) -> int:
     os.makedirs(out_dir, exist_ok=True)
     ir_dir = os.path.join(ROOT, "triton_b200", "ir_programs")
     n = 0
-    for model, consts in MODEL_CONFIGS.items():
-        for fn in sorted(os.listdir(ir_dir)):
-            if not fn.endswith(".txt"):
-                continue
-            text = open(os.path.join(ir_dir, fn)).read().replace("(ploop 0 N D n", f"(ploop 0 N {consts['D']} n")
-            code = TritonCodeGen().generate(IRParser().parse(text), dict(SHAPE_DICT), dict(consts))
+    for fn in sorted(os.listdir(ir_dir)):
+        if not fn.endswith(".txt"):
+            continue
+        program = fn[:-4]
+        for model in (LORA_CONFIGS if program == "lora" else MODEL_CONFIGS):
+            shapes, consts = tables_for(program, model)
+            text = open(os.path.join(ir_dir, fn)).read()
+            if "D" in consts:
+                text = text.replace("(ploop 0 N D n", f"(ploop 0 N {consts['D']} n")
+            code = TritonCodeGen().generate(IRParser().parse(text), dict(shapes), dict(consts))
             compile(code, fn, "exec")      # the emitted module must at least be valid Python
-            with open(os.path.join(out_dir, f"{fn[:-4]}_{model}.py"), "w") as f:
+            with open(os.path.join(out_dir, f"{program}_{model}.py"), "w") as f:
                 f.write(code)
             n += 1
     return n

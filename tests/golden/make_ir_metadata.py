@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
-from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT  # noqa: E402
+from triton_b200.harness import tables_for  # noqa: E402
 
 
 def tree(node):
@@ -36,7 +36,8 @@ def main():
         name = fn[:-4]
         text = open(os.path.join(ir_dir, fn)).read()
         ast = IRParser().parse(text)
-        code = TritonCodeGen().generate(ast, dict(SHAPE_DICT), dict(MODEL_CONFIGS["llama"]))
+        shapes, consts = tables_for(name, "base" if name == "lora" else "llama")
+        code = TritonCodeGen().generate(ast, dict(shapes), dict(consts))
         out[name] = {
             "ast": tree(ast),
             "tensor_params": eval(re.search(r"TENSOR_PARAMS = (.*)", code).group(1)),

@@ -35,7 +35,7 @@ def test_exports_every_declared_symbol(lib):
 def test_struct_layout_matches_header(tmp_path):
     structs = {"TrnRmsArgs": L.TrnRmsArgs, "TrnHeadTensor": L.TrnHeadTensor, "TrnProjArgs": L.TrnProjArgs,
                "TrnAttnArgs": L.TrnAttnArgs, "TrnColStatsArgs": L.TrnColStatsArgs, "TrnTopkArgs": L.TrnTopkArgs,
-               "TrnBlockArgs": L.TrnBlockArgs, "TrnBlockHostArgs": L.TrnBlockHostArgs}
+               "TrnBlockArgs": L.TrnBlockArgs, "TrnBlockHostArgs": L.TrnBlockHostArgs, "TrnLoraArgs": L.TrnLoraArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
     for sname, st in structs.items():
         lines.append(f'  printf("{sname} %zu\\n", sizeof({sname}));')
@@ -61,7 +61,7 @@ def test_error_codes_and_messages(lib):
         assert lib.trinity_strerror(code).decode() not in ("", "unknown error code")
     assert lib.trinity_strerror(-99).decode() == "unknown error code"
     # NULL argument blocks are refused before any CUDA call
-    for fn in (lib.trinity_rmsnorm, lib.trinity_qkv_project, lib.trinity_attention, lib.trinity_attn_colstats,
+    for fn in (lib.trinity_rmsnorm, lib.trinity_qkv_project, lib.trinity_lora, lib.trinity_attention, lib.trinity_attn_colstats,
                lib.trinity_topk, lib.trinity_attn_block, lib.trinity_attn_block_host):
         assert fn(None, None) == -1
     assert lib.trinity_attn_block_workspace(None) == 0

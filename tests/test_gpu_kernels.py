@@ -355,3 +355,34 @@ def test_fused_attention_and_perturbed_lse_equals_two_passes_and_kept_scores_giv
         assert_parity(sp_b, sp_a.cpu(), "KeyFormer sums from kept scores", abs_tol=1e-3 * max(1.0, M / 16), rel_tol=1e-3)
         assert_parity(sp_c, sp_r.cpu(), "RoCo sum p from kept scores", abs_tol=1e-3 * max(1.0, M / 16), rel_tol=1e-3)
         assert_parity(sp2_c, sp2_r.cpu(), "RoCo sum p^2 from kept scores", abs_tol=1e-3 * max(1.0, M / 16), rel_tol=1e-3)
+
+
+@pytest.mark.parametrize("M,N,P,R,dt", (
+    (16, 1024, 512, 64, HF),          # the reference's LoRA configuration (lora_benchmark.py:545)
+    (16, 2048, 1024, 128, HF),        # its "larger model"
+    (200, 520, 320, 64, BF),          # two row tiles, hidden size not a multiple of the 64-wide K step
+    (1, 4096, 4096, 64, BF),          # a single token
+))
+def test_lora_linear_layer(M, N, P, R, dt):
+    """o = x @ w + (x @ a) @ b against the fp32 oracle; d = x @ a is delivered as a 16-bit tensor like the reference's D."""
+    torch.manual_seed(3)
+    x = torch.randn(M, N).to(dt)
+    w, a = (torch.randn(N, P) / N ** 0.5).to(dt), (torch.randn(N, R) / N ** 0.5).to(dt)
+    b = (torch.randn(R, P) / R ** 0.5).to(dt)            # keeps o at unit scale (the tolerance is absolute)
+    o = torch.full((M, P), float("nan"), device="cuda", dtype=dt)
+    d = torch.full((M, R), float("nan"), device="cuda", dtype=dt)
+    ops.lora(x.cuda(), w.cuda(), a.cuda(), b.cuda(), o, d)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    pure = O.lora(x, w, a, b)
+    assert_parity(d, pure["D"], "D = X @ A")
+    # the second step on the D that was stored (one differing bit in D moves a whole row of O slightly)
+    stored = O.lora(x, w, a, b, round_d=dt)
+    like = x.float() @ w.float() + d.float().cpu() @ b.float()
+    assert_parity(o, like, "O on the stored D")
+    assert_parity(o, stored["O"], "O", rel_floor=1e-1, rel_tol=5e-2)
+    o2 = ops.lora(x.cuda(), w.cuda(), a.cuda(), b.cuda())          # allocating form, deterministic
+    torch.cuda.synchronize()
+    assert torch.equal(o2, o)
+    with pytest.raises(L.TrinityError, match="shape"):
+        ops.lora(x.cuda(), w.cuda()[:, :P - 8].contiguous(), a.cuda(), b.cuda()[:, :P - 8].contiguous())

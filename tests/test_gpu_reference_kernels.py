@@ -18,7 +18,7 @@ import torch
 from oracle import attn_block_ref as O
 from triton_b200 import _lib as L
 from triton_b200.convert_module import convert_ir_to_triton
-from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT, AttnBlockBenchmark
+from triton_b200.harness import AttnBlockBenchmark, tables_for
 
 pytestmark = pytest.mark.gpu
 
@@ -27,7 +27,7 @@ REF_DIR = os.path.join(ROOT, "oracle", "_ref")
 IR_DIR = os.path.join(ROOT, "triton_b200", "ir_programs")
 
 CASES = [(p, "llama") for p in ("vanilla", "prenorm", "prenorm_fused", "qknorm", "keyformer", "roco", "rmsnorm")] + \
-        [("vanilla", "falcon"), ("keyformer", "falcon")]
+        [("vanilla", "falcon"), ("keyformer", "falcon"), ("lora", "base"), ("lora", "large")]
 
 
 def _load(path, name):
@@ -41,6 +41,8 @@ def _load(path, name):
 def _outputs(program):
     if program == "rmsnorm":
         return ["X_norm"]
+    if program == "lora":
+        return ["O", "D"]
     outs = ["O2"]
     if program == "keyformer":
         outs.append("C_out")
@@ -55,16 +57,17 @@ def test_against_the_references_generated_kernels(program, model, tmp_path):
     if not os.path.isfile(path):
         pytest.skip("oracle/_ref not generated (needs the reference checkout: python oracle/make_reference_kernels.py)")
     pytest.importorskip("triton")
-    consts = MODEL_CONFIGS[model]
-    M, N, D, H, P = (consts[k] for k in ("M", "N", "D", "H", "P"))
+    shapes, consts = tables_for(program, model)
+    M, N, P = (consts[k] for k in ("M", "N", "P"))
+    D, H = consts.get("D"), consts.get("H")
     ref_mod = _load(path, f"refgen_{program}_{model}")
-    src = convert_ir_to_triton(open(os.path.join(IR_DIR, f"{program}.txt")).read(), SHAPE_DICT, consts)
+    src = convert_ir_to_triton(open(os.path.join(IR_DIR, f"{program}.txt")).read(), shapes, consts)
     our_path = tmp_path / f"ours_{program}_{model}.py"
     our_path.write_text(src)
     our_mod = _load(str(our_path), f"ours_{program}_{model}")
     assert our_mod.TENSOR_PARAMS == ref_mod.TENSOR_PARAMS        # same operator surface, same argument order
 
-    bench = AttnBlockBenchmark(consts, seed=42)
+    bench = AttnBlockBenchmark(consts, seed=42, shape_dict=shapes)
     bench.create_test_tensors(ref_mod.TENSOR_PARAMS)
     T = bench.tensors
     host = {k: v.detach().cpu().clone() for k, v in T.items()}
@@ -76,7 +79,7 @@ def test_against_the_references_generated_kernels(program, model, tmp_path):
         mod.forward(*[T[p] for p in mod.TENSOR_PARAMS])
         torch.cuda.synchronize()
         res = {n: T[n].float().cpu() for n in names}
-        if program != "rmsnorm":
+        if program not in ("rmsnorm", "lora"):
             res["K_new"] = T["K_cache"][:, P:].float().cpu()
         return res
 
@@ -87,6 +90,9 @@ def test_against_the_references_generated_kernels(program, model, tmp_path):
     # fp32 oracle on the same inputs
     if program == "rmsnorm":
         want = {"X_norm": O.rmsnorm(host["X"])}
+    elif program == "lora":
+        r = O.lora(host["X"], host["W"], host["A"], host["B"])
+        want = {"O": r["O"], "D": r["D"]}
     else:
         variant = program.split("_")[0]
         r = O.attn_block(variant, X=host["X"], Wq=host["WQ"], Wk=host["WK"], Wv=host["WV"],

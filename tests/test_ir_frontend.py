@@ -9,7 +9,7 @@ import os
 import pytest
 
 from triton_b200.convert_module import convert_ir_to_triton
-from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT, parse_ir_file, resolve_dim
+from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT, parse_ir_file, resolve_dim, tables_for
 from triton_b200.ir import ASTNode, IRParser, NodeType
 from triton_b200.recognise import recognise
 
@@ -34,7 +34,7 @@ def test_parser_builds_reference_tree(name):
 
 @pytest.mark.parametrize("name", PROGRAMS)
 def test_recogniser_matches_reference_metadata(name):
-    prog = recognise(IRParser().parse(read(name)), SHAPE_DICT)
+    prog = recognise(IRParser().parse(read(name)), tables_for(name, "base" if name == "lora" else "llama")[0])
     assert prog.variant == name.split("_")[0]          # prenorm_fused is a second PreNorm candidate
     assert prog.tensor_params == META[name]["tensor_params"]
     assert prog.block_params == META[name]["block_params"]
@@ -43,7 +43,7 @@ def test_recogniser_matches_reference_metadata(name):
 
 @pytest.mark.parametrize("name", PROGRAMS)
 def test_generated_module_contract(name):
-    src = convert_ir_to_triton(read(name), SHAPE_DICT, MODEL_CONFIGS["llama"])
+    src = convert_ir_to_triton(read(name), *tables_for(name, "base" if name == "lora" else "llama"))
     mod = pyast.parse(src)
     assigned = {t.id for n in mod.body if isinstance(n, pyast.Assign) for t in n.targets}
     assert {"TENSOR_PARAMS", "BLOCK_PARAMS"} <= assigned
@@ -80,11 +80,11 @@ def test_parser_details():
 
 
 def test_recogniser_rejects_foreign_programs():
-    lora = "(store (output O) (* (load (input X) (index fulltile fulltile)) (load (input W) (index fulltile fulltile))) (index fulltile fulltile))"
+    linear = "(store (output O) (* (load (input X) (index fulltile fulltile)) (load (input W) (index fulltile fulltile))) (index fulltile fulltile))"
     with pytest.raises(ValueError):
-        recognise(IRParser().parse(lora), None)
+        recognise(IRParser().parse(linear), None)           # a plain linear layer is none of the operators
     with pytest.raises(ValueError, match="missing from the shape table"):
-        recognise(IRParser().parse(lora), SHAPE_DICT)
+        recognise(IRParser().parse(linear), SHAPE_DICT)
     # an attention program whose result lands in a tensor the operator surface does not know as an output
     broken = read("vanilla").replace("(output O2)", "(output C)")
     with pytest.raises(ValueError, match="no output"):

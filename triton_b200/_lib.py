@@ -25,7 +25,7 @@ VARIANTS = {"vanilla": TRN_VANILLA, "prenorm": TRN_PRENORM, "qknorm": TRN_QKNORM
 # every symbol include/trinity_b200.h declares
 EXPORTS = (
     "trinity_abi_version", "trinity_strerror", "trinity_last_cuda_error", "trinity_last_kernel_status",
-    "trinity_rmsnorm", "trinity_qkv_project", "trinity_attention", "trinity_attention_workspace",
+    "trinity_rmsnorm", "trinity_qkv_project", "trinity_lora", "trinity_attention", "trinity_attention_workspace",
     "trinity_attn_colstats", "trinity_topk",
     "trinity_attn_block_workspace", "trinity_attn_block", "trinity_attn_block_host",
     "trinity_static_scratch_capacity", "trinity_attn_block_static", "trinity_convert", "trinity_probe_mma_rate",
@@ -51,6 +51,13 @@ class TrnProjArgs(C.Structure):
         ("D", C.c_int), ("dtype", C.c_int), ("qk_norm", C.c_int), ("qk_eps", C.c_float),
         ("gamma_q", C.c_void_p), ("gamma_k", C.c_void_p),
         ("q", TrnHeadTensor), ("k_cache", TrnHeadTensor), ("v_cache", TrnHeadTensor),
+    ]
+
+
+class TrnLoraArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("a", C.c_void_p), ("b", C.c_void_p), ("o", C.c_void_p),
+        ("d", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("P", C.c_int), ("R", C.c_int), ("dtype", C.c_int),
     ]
 
 
@@ -140,7 +147,7 @@ def load() -> C.CDLL:
     lib.trinity_last_cuda_error.restype = C.c_char_p
     lib.trinity_last_kernel_status.restype = C.c_int
     lib.trinity_last_kernel_status.argtypes = [C.POINTER(C.c_int)]
-    for name, typ in (("trinity_rmsnorm", TrnRmsArgs), ("trinity_qkv_project", TrnProjArgs),
+    for name, typ in (("trinity_rmsnorm", TrnRmsArgs), ("trinity_qkv_project", TrnProjArgs), ("trinity_lora", TrnLoraArgs),
                       ("trinity_attention", TrnAttnArgs), ("trinity_attn_colstats", TrnColStatsArgs),
                       ("trinity_topk", TrnTopkArgs), ("trinity_attn_block", TrnBlockArgs),
                       ("trinity_attn_block_host", TrnBlockHostArgs), ("trinity_attn_block_static", TrnBlockArgs)):

@@ -47,6 +47,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // launchers implemented per kernel family
 int launch_rmsnorm(const TrnRmsArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_qkv_project(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds);
+int launch_lora(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
 // split-KV policy of the attention kernel: how many CTAs share one tile pair's key range (1: no split),
 // and the scratch a launch of that shape wants for the partial results (0: it would not split)

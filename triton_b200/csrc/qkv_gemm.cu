@@ -62,6 +62,7 @@ struct GemmParams {
   int D;               // head_dim
   int m_tiles, n_tiles_total, total_tiles;
   float qk_eps;
+  int K2;              // KCAT kernels: length of the second contraction phase (0 otherwise)
   int* status;
 };
 
@@ -83,7 +84,10 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
   return c;
 }
 
-template <typename T, int BN>
+// KCAT (LoRA, lora_benchmark.py:41-64: o = x @ w + d @ b with d = x @ a): a single output segment whose
+// accumulator runs over two contraction phases, [x | d] @ [w ; b].  The descriptor slots are reused: tm_w0 = w,
+// tm_w1 = b, tm_w2 = d (an activation like x).  Both products meet in fp32 in tensor memory.
+template <typename T, int BN, bool KCAT>
 __global__ void __launch_bounds__(kThreads, 1)
 qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w0,
                 const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2,
@@ -137,6 +141,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   const int k_steps = (p.K + BK - 1) / BK;
+  const int k_steps2 = KCAT ? (p.K2 + BK - 1) / BK : 0;
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -168,6 +173,25 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
+      if constexpr (KCAT) {
+        // second phase: rows of d against the rows of b that belong to the same output columns
+        for (int ks = 0; ks < k_steps2 && ok; ++ks) {
+          ok = mbar_wait(empty_bar(stage), phase ^ 1u, ctl, KST_TIMEOUT_PRODUCER);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (lane == 0) {
+            const uint32_t sa = smem_base + stage * kStageBytes;
+            const uint32_t sb = sa + kABytes;
+            mbar_expect_tx(full_bar(stage), kStageBytes);
+            tma_load_2d(sa, &tm_w2, full_bar(stage), ks * BK, tc.m_tile * BM);
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * kBBlockBytes, &tm_w1, full_bar(stage), tc.n_tile * BN + c * 64, ks * BK);
+          }
+          __syncwarp();
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
@@ -184,7 +208,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int ks = 0; ks < k_steps; ++ks) {
+      for (int ks = 0; ks < k_steps + k_steps2; ++ks) {
         ok = mbar_wait(full_bar(stage), phase, ctl, KST_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -300,8 +324,15 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   }
 }
 
-template <typename T, int BN>
-int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
+// Extra operands of the LoRA form: o = x @ wq + d @ b (wk, wv unused).
+struct KcatOperands {
+  const void* d;   // [rows, K2]
+  const void* b;   // [K2, heads_q * D]
+  int K2;
+};
+
+template <typename T, int BN, bool KCAT>
+int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, const KcatOperands* kc = nullptr) {
   using Cfg = GemmCfg<BN>;
   GemmParams p{};
   const int rows = a.B * a.M;
@@ -333,11 +364,33 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
     s.row_off = (i == 0) ? 0 : a.P;
     s.norm = (a.qk_norm && i < 2) ? 1 : 0;
     s.gamma = s.norm ? gam[i] : nullptr;
+    if (s.n == 0) {                      // segment not present (single-output forms): placeholder descriptor
+      tm_w[i] = tm_w[0];
+      continue;
+    }
     const uint64_t dims[2] = {static_cast<uint64_t>(s.n), static_cast<uint64_t>(a.N)};
     const uint64_t strides[2] = {1, static_cast<uint64_t>(s.n)};
     const uint32_t box[2] = {64, BK};
     int rc = make_tmap_16bit(&tm_w[i], w[i], 2, dims, strides, box);
     if (rc != TRN_OK) return rc;
+  }
+  if (KCAT) {
+    // slot 1 = b [K2, n0], slot 2 = d [rows, K2]
+    p.K2 = kc->K2;
+    {
+      const uint64_t dims[2] = {static_cast<uint64_t>(p.seg[0].n), static_cast<uint64_t>(kc->K2)};
+      const uint64_t strides[2] = {1, static_cast<uint64_t>(p.seg[0].n)};
+      const uint32_t box[2] = {64, BK};
+      int rc = make_tmap_16bit(&tm_w[1], kc->b, 2, dims, strides, box);
+      if (rc != TRN_OK) return rc;
+    }
+    {
+      const uint64_t dims[2] = {static_cast<uint64_t>(kc->K2), static_cast<uint64_t>(rows)};
+      const uint64_t strides[2] = {1, static_cast<uint64_t>(kc->K2)};
+      const uint32_t box[2] = {BK, BM};
+      int rc = make_tmap_16bit(&tm_w[2], kc->d, 2, dims, strides, box);
+      if (rc != TRN_OK) return rc;
+    }
   }
   p.n_tiles_total = tile0;
   p.total_tiles = p.m_tiles * p.n_tiles_total;
@@ -351,7 +404,7 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
     if (rc != TRN_OK) return rc;
   }
 
-  auto kern = qkv_gemm_kernel<T, BN>;
+  auto kern = qkv_gemm_kernel<T, BN, KCAT>;
   {
     int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes, ds.device);
     if (rc != TRN_OK) return rc;
@@ -371,8 +424,8 @@ int launch_typed(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
   // 37.3 us against 49.6 us).
   const long long m_tiles = (static_cast<long long>(a.B) * a.M + BM - 1) / BM;
   const long long n128 = (a.Hq * a.D + 127) / 128 + 2LL * ((a.Hkv * a.D + 127) / 128);
-  if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128>(a, st, ds);
-  return launch_tiled<T, 256>(a, st, ds);
+  if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, false>(a, st, ds);
+  return launch_tiled<T, 256, false>(a, st, ds);
 }
 
 bool head_tensor_ok(const TrnHeadTensor& t) {
@@ -380,7 +433,50 @@ bool head_tensor_ok(const TrnHeadTensor& t) {
          (t.stride_h & 7) == 0;
 }
 
+// o[M, P] = x[M, N] @ w[N, P] + (x @ a[N, R]) @ b[R, P]: two launches of the projection kernel.  The first writes
+// d = x @ a (16-bit, as the reference's programs keep it); the second runs both contraction phases into one
+// accumulator.  Outputs are addressed as "heads" of 64 columns.
+template <typename T>
+int launch_lora_typed(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds) {
+  auto plain = [&](const void* x, const void* w, void* out, int n_out) {
+    TrnProjArgs pj{};
+    pj.x = x;
+    pj.wq = w; pj.wk = w; pj.wv = w;          // only the first segment exists (Hkv = 0)
+    pj.B = 1; pj.M = a.M; pj.P = 0; pj.N = a.N;
+    pj.Hq = n_out / 64; pj.Hkv = 0; pj.D = 64;
+    pj.dtype = a.dtype;
+    pj.q.ptr = out;
+    pj.q.stride_b = static_cast<int64_t>(a.M) * n_out;
+    pj.q.stride_s = n_out;
+    pj.q.stride_h = 64;
+    pj.k_cache = pj.q;
+    pj.v_cache = pj.q;
+    return pj;
+  };
+  const TrnProjArgs p1 = plain(a.x, a.a, a.d, a.R);
+  int rc = launch_typed<T>(p1, st, ds);
+  if (rc != TRN_OK) return rc;
+  const TrnProjArgs p2 = plain(a.x, a.w, a.o, a.P);
+  const KcatOperands kc{a.d, a.b, a.R};
+  const long long m_tiles = (static_cast<long long>(a.M) + BM - 1) / BM;
+  const long long n128 = (a.P + 127) / 128;
+  if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, true>(p2, st, ds, &kc);
+  return launch_tiled<T, 256, true>(p2, st, ds, &kc);
+}
+
 }  // namespace
+
+int launch_lora(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds) {
+  if (a.x == nullptr || a.w == nullptr || a.a == nullptr || a.b == nullptr || a.o == nullptr || a.d == nullptr)
+    return TRN_E_NULL;
+  if (a.M <= 0 || a.N <= 0 || a.P <= 0 || a.R <= 0) return TRN_E_SHAPE;
+  if ((a.N & 7) != 0 || (a.P & 63) != 0 || (a.R & 63) != 0) return TRN_E_SHAPE;
+  if (!aligned16(a.x) || !aligned16(a.w) || !aligned16(a.a) || !aligned16(a.b) || !aligned16(a.o) || !aligned16(a.d))
+    return TRN_E_ALIGN;
+  if (a.dtype == TRN_BF16) return launch_lora_typed<__nv_bfloat16>(a, st, ds);
+  if (a.dtype == TRN_FP16) return launch_lora_typed<__half>(a, st, ds);
+  return TRN_E_DTYPE;
+}
 
 int launch_qkv_project(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (a.x == nullptr || a.wq == nullptr || a.wk == nullptr || a.wv == nullptr) return TRN_E_NULL;

@@ -58,7 +58,25 @@ SHAPE_DICT: Dict[str, Tuple[str, ...]] = {
     "Q_norm": ("H", "M", "D"), "K_norm": ("H", "M", "D"),
 }
 # inputs get random values, everything else starts at zero (vanilla_llama_benchmark.py:131-139)
-INPUT_TENSORS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise")
+INPUT_TENSORS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise", "W", "A", "B")
+
+# the LoRA harness has a tensor table of its own (lora_benchmark.py:41-64; configurations :545-548)
+LORA_SHAPE_DICT: Dict[str, Tuple[str, ...]] = {
+    "X": ("M", "N"), "W": ("N", "P"), "A": ("N", "R"), "B": ("R", "P"), "O": ("M", "P"),
+    "C": ("M", "P"), "D": ("M", "R"), "E": ("M", "P"),
+}
+LORA_CONFIGS = {
+    "base": {"M": 16, "N": 1024, "P": 512, "R": 64},
+    "large": {"M": 16, "N": 2048, "P": 1024, "R": 128},
+}
+
+
+def tables_for(program: str, model: str):
+    """(shape table, constants) a packaged program is run with: the attention programs on a model's shape, the LoRA
+    program on one of its own configurations."""
+    if program == "lora":
+        return LORA_SHAPE_DICT, LORA_CONFIGS[model]
+    return SHAPE_DICT, MODEL_CONFIGS[model]
 
 
 @dataclass
@@ -92,10 +110,11 @@ def resolve_dim(sym, consts: Dict[str, int]) -> int:
 
 class AttnBlockBenchmark:
     def __init__(self, tensor_config: Dict[str, int], device: Optional[torch.device] = None,
-                 dtype: torch.dtype = torch.float16, seed: Optional[int] = None):
+                 dtype: torch.dtype = torch.float16, seed: Optional[int] = None,
+                 shape_dict: Optional[Dict[str, Tuple[str, ...]]] = None):
         self.tensor_config = dict(tensor_config)
         self.const_dict = dict(tensor_config)
-        self.shape_dict = dict(SHAPE_DICT)
+        self.shape_dict = dict(SHAPE_DICT if shape_dict is None else shape_dict)
         if not torch.cuda.is_available():
             raise RuntimeError("CUDA device not available: the sm_100a kernels have no CPU path")
         self.device = device or torch.device("cuda", torch.cuda.current_device())
@@ -162,6 +181,8 @@ class AttnBlockBenchmark:
             end.record()
         stream.synchronize()
         for out_name in ("O2", "O1", "O", "X_norm"):
+            if out_name not in self.tensors:
+                continue
             if out_name in params and torch.isnan(self.tensors[out_name]).any():
                 raise RuntimeError(f"NaN in {out_name}")
         return start.elapsed_time(end) / benchmark_runs

@@ -115,6 +115,26 @@ def qkv_project(x: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, wv: torch.T
     L.check(L.load().trinity_qkv_project(C.byref(a), _stream()))
 
 
+def lora(x: torch.Tensor, w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, o: Optional[torch.Tensor] = None,
+         d: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """o = x @ w + (x @ a) @ b (lora_benchmark.py:41-64).  x [M, N], w [N, P], a [N, R], b [R, P]; ``d`` [M, R] receives
+    x @ a (allocated when not given: pass it when the call is to be captured in a CUDA graph)."""
+    _need_cuda(x, w, a, b, o, d)
+    M, N = x.shape
+    P, R = w.shape[1], a.shape[1]
+    if w.shape != (N, P) or a.shape != (N, R) or b.shape != (R, P):
+        raise ValueError("lora: expected w [N, P], a [N, R], b [R, P]")
+    o = torch.empty(M, P, dtype=x.dtype, device=x.device) if o is None else o
+    d = torch.empty(M, R, dtype=x.dtype, device=x.device) if d is None else d
+    for t in (x, w, a, b, o, d):
+        if not t.is_contiguous() or t.dtype != x.dtype:
+            raise ValueError("lora: tensors must be contiguous and of one 16-bit dtype")
+    args = L.TrnLoraArgs(x.data_ptr(), w.data_ptr(), a.data_ptr(), b.data_ptr(), o.data_ptr(), d.data_ptr(),
+                         M, N, P, R, _dtype_code(x))
+    L.check(L.load().trinity_lora(C.byref(args), _stream()))
+    return o
+
+
 def _noise_fields(noise: Optional[torch.Tensor]):
     """noise is a (b, h, i, j) view with contiguous j."""
     if noise is None:

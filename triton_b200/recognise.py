@@ -1,7 +1,7 @@
 """Maps a parsed IR program onto the operator the CUDA backend runs for it.
 
 The reference lowers the AST statement by statement into Triton source (TritonGen.py:348-539).  Here
-the AST is only *recognised*: which of the six operators it spells (by the tensor vocabulary of
+the AST is only *recognised*: which of the operators it spells (by the tensor vocabulary of
 convert_eval_rms.py:62-108 and the operations applied to it), which tensors the caller must pass
 (TENSOR_PARAMS, TritonGen.py:563-570) and which block-size keywords the loops imply (BLOCK_PARAMS,
 TritonGen.py:548-556, 571).  Everything the kernels need beyond that comes from the shape and constant
@@ -142,6 +142,12 @@ def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None) -> Pr
     stored = {a.name for a in accesses if a.is_store and a.kind == NodeType.OUTPUT}
 
     has_attention = _has_op(ast, NodeType.EXP) and _has_op(ast, NodeType.MATMUL)
+    if {"X", "W", "A", "B"} <= names and "O" in stored and "K_cache" not in names:
+        # LoRA linear layer (lora_benchmark.py:41-64): O = X @ W + (X @ A) @ B
+        tensor_params = sorted(_memory_resident(accesses))
+        schedule = {"kernels": len(kernels), "in_memory": sorted(n for n in tensor_params if n in ("C", "D", "E")),
+                    "x_norm_in_memory": False, "scores_in_memory": []}
+        return Program("lora", tensor_params, sorted(blocks), names, len(kernels), schedule)
     if "noise" in names:
         variant = "keyformer"
     elif {"C_out1", "C_out2"} & names:

@@ -28,6 +28,10 @@ class BoundOperator:
         self.names = list(spec["tensor_params"])
         self.shapes = {k: _sym(v) for k, v in spec["shapes"].items()}
         c = dict(spec["consts"])
+        self._plans: Dict[Tuple[int, ...], object] = {}
+        self._scratch: Dict[str, torch.Tensor] = {}
+        if self.variant == "lora":          # constants M, N, P, R (lora_benchmark.py:33-36): nothing else to read
+            return
         self.M, self.N, self.D, self.P = c["M"], c["N"], c["D"], c.get("P", 0)
         self.H = c.get("H", self.N // self.D)
         self.B = c.get("B", 1)
@@ -68,6 +72,12 @@ class BoundOperator:
         for name, v in t.items():
             if not isinstance(v, torch.Tensor) or not v.is_cuda:
                 raise ValueError(f"{name}: triton_b200 operators need CUDA tensors (there is no CPU path)")
+        if self.variant == "lora":
+            d = t.get("D")
+            if d is None:
+                d = self._scratch.setdefault("d", torch.empty(t["X"].shape[0], t["A"].shape[1], dtype=t["X"].dtype,
+                                                               device=t["X"].device))
+            return ("lora", t["X"], t["W"], t["A"], t["B"], t["O"], d)
         if self.variant == "rmsnorm":
             x = t["X"]
             gamma = t.get("gamma")
@@ -104,8 +114,8 @@ class BoundOperator:
             kw.update(sum_p=t["C_out1"], sum_p2=t["C_out2"])
         return ("block", ops.BlockPlan(self.variant, **kw))
 
-    _INPUTS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise", "gamma", "gamma_q", "gamma_k")
-    _OUTPUTS = ("O2", "O1", "O", "Q", "Q_norm", "K_cache", "V_cache", "C_out", "C_out1", "C_out2", "X_norm")
+    _INPUTS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise", "gamma", "gamma_q", "gamma_k", "W", "A", "B")
+    _OUTPUTS = ("O2", "O1", "O", "Q", "Q_norm", "K_cache", "V_cache", "C_out", "C_out1", "C_out2", "X_norm", "D")
 
     def _bind_any(self, tensors: Sequence[torch.Tensor]):
         """fp32 callers (the fp32 Vanilla configuration): 16-bit shadows of every tensor are allocated at
@@ -131,7 +141,10 @@ class BoundOperator:
         plan, pairs_in, pairs_out = bound
         for src, dst in pairs_in:
             ops.convert(src.contiguous(), dst)
-        if plan[0] == "rms":
+        if plan[0] == "lora":
+            _, x, w, a, b, o, d = plan
+            ops.lora(x, w, a, b, o, d)
+        elif plan[0] == "rms":
             _, x, y, gamma, x2 = plan
             ops.rmsnorm(x, gamma, self.eps, out=y)
         else:
