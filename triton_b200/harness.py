@@ -229,9 +229,10 @@ def find_best_kernels(results: List[BenchmarkResult], top_k: int = 10) -> List[B
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(description="Benchmark IR candidates of one attention-block variant")
-    ap.add_argument("--variant", choices=VARIANTS, default="vanilla")
-    ap.add_argument("--model", choices=sorted(MODEL_CONFIGS), default="llama")
+    ap = argparse.ArgumentParser(description="Benchmark IR candidates of one attention-block variant (or the LoRA layer)")
+    ap.add_argument("--variant", choices=VARIANTS + ("prenorm_fused", "lora"), default="vanilla")
+    ap.add_argument("--model", choices=sorted(MODEL_CONFIGS) + sorted(LORA_CONFIGS), default=None,
+                    help="llama / falcon for the attention programs (default llama); base / large for lora (default base)")
     ap.add_argument("--ir", type=str, default=None, help="IR candidates file (default: the packaged program)")
     ap.add_argument("--tensors", type=str, default=None, help="JSON list of {M,N,D,H,P} (default: the model's)")
     ap.add_argument("--output", type=str, default=None)
@@ -243,11 +244,13 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
 
     ir_file = args.ir or str(IR_DIR / f"{args.variant}.txt")
-    configs = json.loads(Path(args.tensors).read_text()) if args.tensors else [MODEL_CONFIGS[args.model]]
-    output = args.output or f"{args.variant}_{args.model}.json"
+    model = args.model or ("base" if args.variant == "lora" else "llama")
+    shapes, default_cfg = tables_for(args.variant, model)
+    configs = json.loads(Path(args.tensors).read_text()) if args.tensors else [default_cfg]
+    output = args.output or f"{args.variant}_{model}.json"
     all_results: List[BenchmarkResult] = []
     for cfg in configs:
-        bench = AttnBlockBenchmark(cfg)
+        bench = AttnBlockBenchmark(cfg, shape_dict=shapes)
         res = bench.run_all_benchmarks(ir_file, args.start, args.num, args.end)
         bench.cleanup()
         all_results.extend(res)
