@@ -12,8 +12,11 @@
 //   * MHA: two consecutive key blocks of one head.
 //   warp 0      TMA producer: both k tiles once, then both tiles' q blocks through a ring
 //   warp 1      one lane issues tcgen05.mma  S^T_t = k_t q_t^T  into two TMEM buffers per tile
-//   warps 2-5   statistics warpgroup of tile 0, warps 6-9 of tile 1; thread = key:
-//               p = 2^(t - lse_query), accumulate sum p and sum p^2 (packed fp32x2 arithmetic)
+//   warps 2-17  four statistics warpgroups, two per tile; thread = key, and the two warpgroups of a tile
+//               split every query block's columns in halves (64 queries each): 16 arithmetic warps per SM
+//               instead of 8 keep the issue slots and the XU pipe busy while others wait on a result.
+//               p = 2^(t - lse_query), accumulate sum p and sum p^2 (packed fp32x2 arithmetic); the second
+//               half's sums are added to the first's through shared memory at the end (fixed order)
 #include <math.h>
 
 #include <type_traits>
@@ -25,7 +28,8 @@ namespace {
 
 constexpr int BKEY = 128;
 constexpr int BQRY = 128;
-constexpr int kCsThreads = 320;
+constexpr int kCsHalves = 2;           // statistics warpgroups per key tile
+constexpr int kCsThreads = 64 + 2 * kCsHalves * 128;
 constexpr int kCsTmemCols = 512;      // tile t, buffer u: columns [(2t+u)*128, +128)
 
 struct CsParams {
@@ -51,9 +55,10 @@ struct CsSmem {
   static constexpr int kTileBytes = kChunks * kChunkBytes;
   static constexpr int kKOff = 0;                                     // two k tiles
   static constexpr int kQOff = 2 * kTileBytes;                        // ring of (q tile 0, q tile 1)
-  static constexpr int kLseOff = kQOff + kStages * 2 * kTileBytes;    // 8 warps x 2 buffers x 128 floats
-  static constexpr int kHashOff = kLseOff + 8 * 2 * 128 * 4;          // same shape: per-query noise row hashes
-  static constexpr int kBarOff = kHashOff + 8 * 2 * 128 * 4;
+  static constexpr int kLseOff = kQOff + kStages * 2 * kTileBytes;    // 16 warps x 2 buffers x 64 floats
+  static constexpr int kHashOff = kLseOff + 16 * 2 * 64 * 4;          // same shape: per-query noise row hashes
+  static constexpr int kPartOff = kHashOff + 16 * 2 * 64 * 4;         // second half's sums: 2 tiles x 128 keys x 2
+  static constexpr int kBarOff = kPartOff + 2 * 128 * 2 * 4;
   static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
@@ -100,7 +105,7 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     for (int t = 0; t < 2; ++t)
       for (int u = 0; u < 2; ++u) {
         mbar_init(s_full(t, u), 1);
-        mbar_init(s_free(t, u), 128);
+        mbar_init(s_free(t, u), 128 * kCsHalves);
       }
     *abort_flag = 0;
     fence_mbar_init();
@@ -210,15 +215,17 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       __syncwarp();
     }
   } else {
-    const int t = (warp - 2) >> 2;
+    const int t = ((warp - 2) >> 2) & 1;
+    const int hf = (warp - 2) >> 3;              // which half of a query block's columns
     const int quad = warp & 3;
     const int row = quad * 32 + lane;            // key within the tile
     const int key = tile[t].k0 + row;
     const int h = tile[t].h;
     const bool present = tile[t].present != 0;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    float* my_lse = lse_s + ((warp - 2) * 2) * 128;
-    uint32_t* my_hash = hash_s + ((warp - 2) * 2) * 128;
+    float* my_lse = lse_s + ((warp - 2) * 2) * 64;
+    uint32_t* my_hash = hash_s + ((warp - 2) * 2) * 64;
+    float2* part = reinterpret_cast<float2*>(smem_gen + SM::kPartOff) + t * 128 + row;
     const uint32_t headkey = PERT ? noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)) : 0u;
     float2 acc1 = make_float2(0.f, 0.f), acc2 = make_float2(0.f, 0.f);
     bool ok = true;
@@ -227,17 +234,19 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     for (int it = 0; it < n_iter && present; ++it) {
       const int u = it & 1;
       const int q0 = (i_start + it) * BQRY;
-      float* nl = my_lse + u * 128;
+      // staged values are indexed by the block's column: this warp holds columns [64 hf, 64 hf + 64)
+      float* nl = my_lse + u * 64 - hf * 64;
+      const uint32_t* hrow = my_hash + u * 64 - hf * 64;
       {
-        // each warp stages its own copy of this block's per-query NEGATED log-sum-exp (no cross-warp
+        // each warp stages its own copy of its columns' per-query NEGATED log-sum-exp (no cross-warp
         // barrier); -inf for queries past M makes their p = 0
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
+        for (int v = 2 * hf; v < 2 * hf + 2; ++v) {
           const int q = q0 + v * 32 + lane;
           float val = -INFINITY;
           if (q < p.M) val = -__ldg(p.lse + (static_cast<long long>(b) * p.Hq + h) * p.M + q);
           nl[v * 32 + lane] = val;
-          if (PERT) my_hash[u * 128 + v * 32 + lane] = noise_rowhash(headkey, static_cast<uint32_t>(q));
+          if (PERT) my_hash[u * 64 - hf * 64 + v * 32 + lane] = noise_rowhash(headkey, static_cast<uint32_t>(q));
         }
         __syncwarp();
       }
@@ -247,40 +256,47 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_after();
       const uint32_t s_tmem = tmem_base + (2 * t + u) * BQRY + lane_addr;
       // 32-query chunks that hold at least one query (M = 16 new tokens: one chunk instead of four)
-      const int n_chunks = min(BQRY / 32, (p.M - q0 + 31) / 32);
+      const int c_begin = 2 * hf;
+      const int n_chunks = min(2 * hf + 2, (p.M - q0 + 31) / 32);          // one past this warp's last chunk
       // causal: this key is visible to query q0 + col iff col >= key - P - q0
       const int cmin = p.causal ? (key - p.P - q0) : 0;
       const bool masked = p.causal && (tile[t].k0 + BKEY - 1 - p.P > q0);
-      if (PERT && !masked && p.noise.mode == TRN_NOISE_GUMBEL) {   // warp-uniform: rows past L just compute unused values
-        // interior block, generated noise: the per-key part of the hash is a thread constant, the
-        // per-query part comes from shared memory four at a time
+      if (PERT && p.noise.mode == TRN_NOISE_GUMBEL) {   // warp-uniform: rows past L just compute unused values
+        // generated noise: the per-key part of the hash is a thread constant, the per-query part comes from
+        // shared memory four at a time.  Queries past M have -lse = -inf and give p = 0; compiled twice so
+        // that only the block on the causal diagonal carries the per-element compare
         const uint32_t jc = static_cast<uint32_t>(key) * 0x85ebca6bu;
         const float c_s = p.scale * p.pert_log2;
         const float c_g = -0.6931471805599453f * p.pert_log2;
-        const uint32_t* hrow = my_hash + u * 128;
+        auto gumbel_block = [&](auto masked_tag) {
+          constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll 1
-        for (int c = 0; c < n_chunks; ++c) {
-          tmem_ld32(s_tmem + c * 32, r);
-          tmem_wait_ld();
+          for (int c = c_begin; c < n_chunks; ++c) {
+            tmem_ld32(s_tmem + c * 32, r);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const uint4 h4 = *reinterpret_cast<const uint4*>(hrow + c * 32 + i);
-            const float4 n4 = *reinterpret_cast<const float4*>(nl + c * 32 + i);
-            const uint32_t hh[4] = {h4.x, h4.y, h4.z, h4.w};
-            const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
+            for (int i = 0; i < 32; i += 4) {
+              const uint4 h4 = *reinterpret_cast<const uint4*>(hrow + c * 32 + i);
+              const float4 n4 = *reinterpret_cast<const float4*>(nl + c * 32 + i);
+              const uint32_t hh[4] = {h4.x, h4.y, h4.z, h4.w};
+              const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              uint32_t x = hh[e] ^ jc;
-              x ^= x >> 16; x *= 0x7feb352du;
-              x ^= x >> 15;
-              const float tt = fmaf(gumbel_log2e_from_bits(x), c_g, fmaf(__uint_as_float(r[i + e]), c_s, nn[e]));
-              const float pr = ex2_approx(tt);
-              if (e & 1) acc1.y += pr; else acc1.x += pr;
+              for (int e = 0; e < 4; ++e) {
+                uint32_t x = hh[e] ^ jc;
+                x ^= x >> 16; x *= 0x7feb352du;
+                x ^= x >> 15;
+                const float tt = fmaf(gumbel_log2e_from_bits(x), c_g, fmaf(__uint_as_float(r[i + e]), c_s, nn[e]));
+                float pr = ex2_approx(tt);
+                if (kMasked && c * 32 + i + e < cmin) pr = 0.f;
+                if (e & 1) acc1.y += pr; else acc1.x += pr;
+              }
             }
           }
-        }
-      } else if (PERT || masked) {
-        for (int c = 0; c < n_chunks; ++c) {
+        };
+        if (masked) gumbel_block(std::true_type{});
+        else gumbel_block(std::false_type{});
+      } else if (PERT) {
+        for (int c = c_begin; c < n_chunks; ++c) {
           tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
 #pragma unroll
@@ -289,7 +305,7 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             float tt;
             if (PERT) {
               const int q = q0 + col;
-              const float g = (q < p.M && key < p.L) ? noise_at<T>(p.noise, my_hash[u * 128 + col], b, h, q, key) : 0.f;
+              const float g = (q < p.M && key < p.L) ? noise_at<T>(p.noise, hrow[col], b, h, q, key) : 0.f;
               tt = (__uint_as_float(r[i]) * p.scale + g) * p.pert_log2;
             } else {
               tt = __uint_as_float(r[i]) * p.scale_log2;
@@ -301,31 +317,47 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
       } else {
+        auto plain_block = [&](auto masked_tag) {
+          constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll 1
-        for (int c = 0; c < n_chunks; ++c) {
-          tmem_ld32(s_tmem + c * 32, r);
-          tmem_wait_ld();
+          for (int c = c_begin; c < n_chunks; ++c) {
+            tmem_ld32(s_tmem + c * 32, r);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 n4 = *reinterpret_cast<const float4*>(nl + c * 32 + i);
-            const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2,
-                                         make_float2(n4.x, n4.y));
-            const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), c2,
-                                         make_float2(n4.z, n4.w));
-            const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
-            const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
-            acc1 = __fadd2_rn(acc1, p0);
-            acc2 = __ffma2_rn(p0, p0, acc2);
-            acc1 = __fadd2_rn(acc1, p1);
-            acc2 = __ffma2_rn(p1, p1, acc2);
+            for (int i = 0; i < 32; i += 4) {
+              const float4 n4 = *reinterpret_cast<const float4*>(nl + c * 32 + i);
+              const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2,
+                                           make_float2(n4.x, n4.y));
+              const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), c2,
+                                           make_float2(n4.z, n4.w));
+              float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+              float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+              if constexpr (kMasked) {
+                const int col = c * 32 + i;
+                if (col < cmin) p0.x = 0.f;
+                if (col + 1 < cmin) p0.y = 0.f;
+                if (col + 2 < cmin) p1.x = 0.f;
+                if (col + 3 < cmin) p1.y = 0.f;
+              }
+              acc1 = __fadd2_rn(acc1, p0);
+              acc2 = __ffma2_rn(p0, p0, acc2);
+              acc1 = __fadd2_rn(acc1, p1);
+              acc2 = __ffma2_rn(p1, p1, acc2);
+            }
           }
-        }
+        };
+        if (masked) plain_block(std::true_type{});
+        else plain_block(std::false_type{});
       }
       tc_fence_before();
       mbar_arrive(s_free(t, u));
     }
-    if (ok && present && key < p.L) {
-      const float a1 = acc1.x + acc1.y, a2 = acc2.x + acc2.y;
+    // the second half hands its sums to the first, which owns the key's output
+    if (hf == 1) *part = make_float2(acc1.x + acc1.y, acc2.x + acc2.y);
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "n"(128 * kCsHalves) : "memory");
+    if (hf == 0 && ok && present && key < p.L) {
+      const float2 other = *part;
+      const float a1 = (acc1.x + acc1.y) + other.x, a2 = (acc2.x + acc2.y) + other.y;
       const long long o = (static_cast<long long>(b) * p.Hq + h) * p.L + key;
       if (p.stats_fp32) {
         static_cast<float*>(p.sum_p)[o] = a1;
