@@ -387,13 +387,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool noise_pre_ok = false;
     // Perturbed scores of chunk c of block kv0 (S values in r[]): online log-sum-exp update, optional write-out.
     // t = (s * scale + g) * log2(e) / tau; with generated noise g = -ln2 * log2(E):  t = s * c_s + log2(E) * c_g
+    //
+    // The exponentials of a chunk are DEFERRED to the next call: tv[] keeps the chunk's perturbed scores and
+    // pend_m the maximum they are to be taken against, and the next chunk's generator (integer and lg2 work)
+    // runs between them, so that the XU pipe and the other pipes stay busy together instead of in turns.
+    // l2_run is relative to m_l, the maximum of the last chunk folded in; pert_flush() folds the last one.
+    float tv[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) tv[i] = -INFINITY;
+    float pend_m = -INFINITY, m_l = -INFINITY;
+    auto pert_fold = [&](float accp) {
+      if (pend_m != -INFINITY) {
+        l2_run = l2_run * ex2_approx(m_l - pend_m) + accp;      // m_l = -inf, l2_run = 0 on the first fold
+        m_l = pend_m;
+      }
+    };
+    auto pert_flush = [&]() {
+      const float sub = (pend_m == -INFINITY) ? 0.f : pend_m;
+      float accp = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) accp += ex2_approx(tv[i] - sub);
+      pert_fold(accp);
+      pend_m = -INFINITY;
+      m2_run = m_l;
+    };
     auto pert_chunk = [&](int kv0, int c, bool masked) {
       const bool fast = p.noise.mode == TRN_NOISE_GUMBEL;
+      const float sub = (pend_m == -INFINITY) ? 0.f : pend_m;     // tv[] = -inf then: every term is 0
+      float accp = 0.f;
       // 128-bit loads need the noise rows 16-byte aligned (checked once on the host)
       const bool fast_tensor = !masked && p.noise.mode == TRN_NOISE_TENSOR && p.noise_vec_ok;
       const float c_s = p.scale * p.pert_log2;
       const float c_g = -0.6931471805599453f * p.pert_log2;
-      float tv[32];
       float cm = -INFINITY;
       if (fast) {
         // generated noise, no per-element compare.  Written stage by stage over groups of eight keys: with two
@@ -414,6 +439,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int i = 0; i < G; ++i) x[i] *= 0x7feb352du;
 #pragma unroll
           for (int i = 0; i < G; ++i) x[i] = (x[i] ^ (x[i] >> 15)) >> 9;
+#pragma unroll
+          for (int i = 0; i < G; ++i) accp += ex2_approx(tv[i0 + i] - sub);      // the previous chunk's
 #pragma unroll
           for (int i = 0; i < G; ++i) u[i] = lg2_approx(unit_from_23bits(x[i]));
 #pragma unroll
@@ -442,6 +469,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       } else if (fast_tensor) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) accp += ex2_approx(tv[i] - sub);
         // interior block, noise tensor: this row's 32 values come in as four 128-bit loads
         const T* nrow = static_cast<const T*>(p.noise.ptr) + b * p.noise.sb + h * p.noise.sh +
                         static_cast<long long>(row_valid ? q_abs : 0) * p.noise.si + kv0 + c * 32;
@@ -461,6 +490,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       } else {
 #pragma unroll
+        for (int i = 0; i < 32; ++i) accp += ex2_approx(tv[i] - sub);
+#pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int col = kv0 + c * 32 + i;
           float v = -INFINITY;
@@ -472,14 +503,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           cm = fmaxf(cm, v);
         }
       }
-      const float m_new = fmaxf(m2_run, cm);
-      if (m_new != -INFINITY) {
-        float acc = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc += ex2_approx(tv[i] - m_new);
-        l2_run = l2_run * ex2_approx(m2_run - m_new) + acc;
-        m2_run = m_new;
-      }
+      pert_fold(accp);
+      m2_run = fmaxf(m2_run, cm);
+      pend_m = m2_run;            // -inf while the row has seen no visible key: tv[] is all -inf then
       if (score_row != nullptr && kv0 + c * 32 < p.score_pitch) {
 #pragma unroll
         for (int i = 0; i < 32; i += 4)
@@ -679,6 +705,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool split_out = p.n_splits > 1;
     const long long part_row =
         ((static_cast<long long>(split) * p.B + b) * p.Hq + h) * p.M + q_abs;   // row of the partial results
+    if constexpr (kPert) pert_flush();
     if (MODE == 1) { m_run = m2_run; l_run = l2_run; }        // MODE 1 reports the perturbed value as its lse
     if constexpr (DUP) {
       // ---- merge the four replicas of this tile inside the CTA.  The k / v stages and the q tiles are free once
