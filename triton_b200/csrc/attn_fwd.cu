@@ -652,45 +652,87 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // compiled twice: the unmasked version carries no per-element compare / select
       auto pass2 = [&](auto masked_tag) {
         constexpr bool kMasked = decltype(masked_tag)::value;
-#pragma unroll 1
-        for (int c = 0; c < BKV / 32; ++c) {
-          uint32_t pk[SPLIT ? 32 : 16];
-          if (my_chunk(c)) {
-            if (!r_holds_s) {          // warp-uniform
-              tmem_ld32(s_tmem + c * 32, r);
-              tmem_wait_ld();
-            }
+        // p of the 32 score columns of chunk c held in src[] -> pk[] (hi parts, then lo parts), row sum
+        auto chunk_p = [&](const uint32_t (&src)[32], int c, uint32_t (&pk)[SPLIT ? 32 : 16]) {
+          // stage by stage over groups of eight column pairs: one softmax warp per scheduler is active at a
+          // time, so the order of independent instructions decides how much of each result's latency is hidden
+          constexpr int G = 8;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, neg_m2);
-              float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-              if constexpr (kMasked) {
-                if (kv0 + c * 32 + i > limit) pp.x = 0.f;
-                if (kv0 + c * 32 + i + 1 > limit) pp.y = 0.f;
-              }
-              lsum = __fadd2_rn(lsum, pp);
-              const uint32_t hi = Io<T>::pack2(pp.x, pp.y);
-              pk[i >> 1] = hi;
-              if constexpr (SPLIT) {
-                // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
-                const float2 lo = __ffma2_rn(Io<T>::unpack2(hi), minus1, pp);    // p - hi, exact
-                pk[16 + (i >> 1)] = Io<T>::pack2(lo.x, lo.y);
+          for (int i0 = 0; i0 < 16; i0 += G) {
+            float2 pp[G];
+#pragma unroll
+            for (int i = 0; i < G; ++i)
+              pp[i] = __ffma2_rn(make_float2(__uint_as_float(src[2 * (i0 + i)]), __uint_as_float(src[2 * (i0 + i) + 1])),
+                                 c2, neg_m2);
+#pragma unroll
+            for (int i = 0; i < G; ++i) pp[i] = make_float2(ex2_approx(pp[i].x), ex2_approx(pp[i].y));
+            if constexpr (kMasked) {
+#pragma unroll
+              for (int i = 0; i < G; ++i) {
+                if (kv0 + c * 32 + 2 * (i0 + i) > limit) pp[i].x = 0.f;
+                if (kv0 + c * 32 + 2 * (i0 + i) + 1 > limit) pp[i].y = 0.f;
               }
             }
-          } else {
-            // another replica's columns: this replica's p is zero there
 #pragma unroll
-            for (int i = 0; i < (SPLIT ? 32 : 16); ++i) pk[i] = 0u;
+            for (int i = 0; i < G; ++i) pk[i0 + i] = Io<T>::pack2(pp[i].x, pp[i].y);
+#pragma unroll
+            for (int i = 0; i < G; ++i) lsum = __fadd2_rn(lsum, pp[i]);
+            if constexpr (SPLIT) {
+              // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
+#pragma unroll
+              for (int i = 0; i < G; ++i) pp[i] = __ffma2_rn(Io<T>::unpack2(pk[i0 + i]), minus1, pp[i]);   // p - hi, exact
+#pragma unroll
+              for (int i = 0; i < G; ++i) pk[16 + i0 + i] = Io<T>::pack2(pp[i].x, pp[i].y);
+            }
           }
+        };
+        auto store_p = [&](int c, uint32_t (&pk)[SPLIT ? 32 : 16]) {
           if constexpr (SPLIT) {
             tmem_st32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(pk));
           } else {
             tmem_st16(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[16]>(pk));
           }
-          if (c == 1) {            // keys 0..63 of P are written: let P v begin
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(p_ready(t, 0));
+        };
+        auto first_half_ready = [&]() {        // keys 0..63 of P are written: let P v begin
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(p_ready(t, 0));
+        };
+        if constexpr (DUP) {
+#pragma unroll 1
+          for (int c = 0; c < BKV / 32; ++c) {
+            uint32_t pk[SPLIT ? 32 : 16];
+            if (my_chunk(c)) {
+              if (!r_holds_s) {          // warp-uniform
+                tmem_ld32(s_tmem + c * 32, r);
+                tmem_wait_ld();
+              }
+              chunk_p(r, c, pk);
+            } else {
+              // another replica's columns: this replica's p is zero there
+#pragma unroll
+              for (int i = 0; i < (SPLIT ? 32 : 16); ++i) pk[i] = 0u;
+            }
+            store_p(c, pk);
+            if (c == 1) first_half_ready();
+          }
+        } else {
+          // two register buffers: the tensor-memory load of the next chunk is in flight while this one is worked on
+          uint32_t rb[32];
+          tmem_ld32(s_tmem, r);
+          tmem_wait_ld();
+#pragma unroll 1
+          for (int c = 0; c < BKV / 32; c += 2) {
+            uint32_t pk[SPLIT ? 32 : 16];
+            tmem_ld32(s_tmem + (c + 1) * 32, rb);
+            chunk_p(r, c, pk);
+            store_p(c, pk);
+            tmem_wait_ld();
+            if (c + 2 < BKV / 32) tmem_ld32(s_tmem + (c + 2) * 32, r);
+            chunk_p(rb, c + 1, pk);
+            store_p(c + 1, pk);
+            if (c == 0) first_half_ready();
+            tmem_wait_ld();
           }
         }
       };
