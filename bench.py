@@ -39,6 +39,8 @@ WORKLOADS = {
     "qknorm_falcon": dict(variant="qknorm", B=4, S=2048, N=4544, Hq=71, Hkv=1, D=64, project=True, topk=0),
     "keyformer_llama": dict(variant="keyformer", B=4, S=4096, N=0, Hq=32, Hkv=8, D=128, project=False, topk=1024),
     "roco_falcon": dict(variant="roco", B=2, S=8192, N=0, Hq=71, Hkv=1, D=64, project=False, topk=2048),
+    # one batch item of the KeyFormer workload: the size used for ncu captures of its two passes
+    "keyformer_llama_b1": dict(variant="keyformer", B=1, S=4096, N=0, Hq=32, Hkv=8, D=128, project=False, topk=1024),
     # standalone RMSNorm (HBM-bound): rows x cols, bf16, eps 1e-5, gamma
     "rmsnorm_llama": dict(variant="rmsnorm", rows=16384, cols=4096),
     "rmsnorm_falcon": dict(variant="rmsnorm", rows=8192, cols=4544),
