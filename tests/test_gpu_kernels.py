@@ -362,6 +362,8 @@ def test_fused_attention_and_perturbed_lse_equals_two_passes_and_kept_scores_giv
     (16, 2048, 1024, 128, HF),        # its "larger model"
     (200, 520, 320, 64, BF),          # two row tiles, hidden size not a multiple of the 64-wide K step
     (1, 4096, 4096, 64, BF),          # a single token
+    (9, 1024, 512, 128, BF),          # a partial row block on the path for at most 16 tokens
+    (17, 1024, 512, 64, HF),          # one token too many for it: the tiled kernels
 ))
 def test_lora_linear_layer(M, N, P, R, dt):
     """o = x @ w + (x @ a) @ b against the fp32 oracle; d = x @ a is delivered as a 16-bit tensor like the reference's D."""

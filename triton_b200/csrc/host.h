@@ -48,6 +48,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int launch_rmsnorm(const TrnRmsArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_qkv_project(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_lora(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds);
+// at most 16 tokens: one latency-oriented launch (lora_small.cu); callers validate the arguments first
+bool lora_small_applies(const TrnLoraArgs& a);
+int launch_lora_small(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
 // split-KV policy of the attention kernel: how many CTAs share one tile pair's key range (1: no split),
 // and the scratch a launch of that shape wants for the partial results (0: it would not split)

@@ -473,6 +473,8 @@ int launch_lora(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds) {
   if ((a.N & 7) != 0 || (a.P & 63) != 0 || (a.R & 63) != 0) return TRN_E_SHAPE;
   if (!aligned16(a.x) || !aligned16(a.w) || !aligned16(a.a) || !aligned16(a.b) || !aligned16(a.o) || !aligned16(a.d))
     return TRN_E_ALIGN;
+  if (a.dtype != TRN_BF16 && a.dtype != TRN_FP16) return TRN_E_DTYPE;
+  if (lora_small_applies(a)) return launch_lora_small(a, st, ds);
   if (a.dtype == TRN_BF16) return launch_lora_typed<__nv_bfloat16>(a, st, ds);
   if (a.dtype == TRN_FP16) return launch_lora_typed<__half>(a, st, ds);
   return TRN_E_DTYPE;
