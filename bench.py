@@ -496,6 +496,27 @@ def run_native(args, w):
         err = None
     except Exception as e:                       # the reference's QKNorm kernels overflow fp16 at these inputs
         ms, err = float("nan"), str(e)
+    # the harness's event pairs around one replay resolve about 2 us; a second figure with 20 calls per captured
+    # graph and one event pair around 50 replays separates operators that take a few microseconds
+    us_batched = None
+    if err is None:
+        tensors = [bench.tensors[name] for name in mod.TENSOR_PARAMS]
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    mod.forward(*tensors)
+            side.synchronize()
+            for _ in range(3):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            for _ in range(50):
+                graph.replay()
+            e1.record(side)
+        side.synchronize()
+        us_batched = e0.elapsed_time(e1) / (50 * 20) * 1e3
     clocks = sampler.stop()
     if prog == "rmsnorm":
         flops = 3 * M * N
@@ -505,7 +526,8 @@ def run_native(args, w):
     else:
         flops = 2 * M * N * 3 * H * D + 4 * H * D * M * (P + M)
     line = dict(base, value=None if err else flops / (ms * 1e-3) / 1e12, steps=100, warmup=10,
-                ms_per_step=None if err else ms, us_per_call=None if err else ms * 1e3, clocks=clocks,
+                ms_per_step=None if err else ms, us_per_call=None if err else ms * 1e3,
+                us_per_call_20_per_graph=us_batched, clocks=clocks,
                 gpu_launches=100, e2e=None)
     if err:
         line["error"] = err
