@@ -91,6 +91,10 @@ __device__ __forceinline__ void st_cluster_f2(uint32_t addr, float a, float b) {
 }
 // hardware barrier over every thread of the cluster (no spinning; all CTAs of a cluster are co-scheduled and no
 // thread of this kernel returns before its last barrier)
+// the same barrier without the release fence: for "I am done reading", where the arriving CTA publishes nothing
+__device__ __forceinline__ void cluster_sync_all_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -253,7 +257,9 @@ lora_small_kernel(const LsParams p) {
       wsum[j].y += v.y;
     }
   }
-  cluster_sync_all();        // every CTA of the cluster is past its ring: rank 0's exchange area may be written
+  // every CTA of the cluster is past its ring (its cp.async groups are complete and the values read above are in
+  // registers): rank 0's exchange area may be written.  Nothing is published here, so no release fence
+  cluster_sync_all_relaxed();
   {
     const uint32_t slot = map_to_rank(smem_base + SM::kXchg, 0) + rank * (16 * SM::kXchgRow * 4);
 #pragma unroll
