@@ -63,6 +63,16 @@ const char* trinity_last_cuda_error(void);
 /* Device-side status word of the current device: 0 when every kernel launched so far finished its
  * waits in time.  SYNCHRONISES the device (it reads device memory); call it outside timed regions. */
 int trinity_last_kernel_status(int* status_out);
+/* The status word is sticky: once a wait ran out, every later kernel of the library on that device returns at
+ * once and trinity_last_kernel_status() keeps reporting TRN_E_KERNEL.  This resets it to 0 (SYNCHRONISES the
+ * device) after the caller has dealt with the failure. */
+int trinity_clear_kernel_status(void);
+/* Self-test of that failure path, no reference counterpart (the reference has no device-side failure handling;
+ * its harness only catches Python exceptions, vanilla_llama_benchmark.py:329-332): launches one tiny kernel whose
+ * only wait is on a barrier nothing arrives at, limited to `limit_us` microseconds (1 .. 100000).  The kernel
+ * returns normally — it frees its tensor memory, does not trap and does not spin on — and leaves code 103 in
+ * the status word: trinity_last_kernel_status() then returns TRN_E_KERNEL until trinity_clear_kernel_status(). */
+int trinity_selftest_wait_timeout(int limit_us, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Standalone RMSNorm:  y[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * gamma[:]
@@ -248,7 +258,8 @@ int trinity_convert(const void* src, void* dst, int64_t n, int dtype16, int to_f
  * would fill less than half of the SMs) and, for KeyFormer / RoCo problems whose [B,Hq,M,P+M] fp32 scores fit in
  * 32 MiB, those scores (the statistics are then summed from memory instead of a second q k^T pass).
  * trinity_attn_block_workspace() returns required + optional; any size from the required part upwards is accepted.
- * skip_projection != 0: q / k_cache / v_cache are taken as given (BASELINE configs 4 and 5).
+ * skip_projection != 0: q / k_cache / v_cache are taken as given (callers that hold projected Q / K / V already,
+ * as the KeyFormer and RoCo long-context configurations do).
  * ---------------------------------------------------------------------------------------------- */
 typedef struct {
   int variant;
@@ -324,12 +335,17 @@ int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream);
  * inside the library: trinity_static_scratch_capacity() bytes (8 MiB), held by every GPU that loads the
  * library until the process exits.
  *
- * Same arguments and results as trinity_attn_block; `workspace` / `workspace_bytes` are ignored.  x_norm
- * (PreNorm with gamma) is still the caller's.  The call performs no cudaMalloc / cudaFree and calls no
- * allocating routine.  Limits and rules:
- *   - a problem whose trinity_attn_block_workspace() exceeds the capacity is refused with
- *     TRN_E_STATIC_SCRATCH and nothing is launched (capacity covers B*M*(1+2*Hq) fp32 values up to ~2 M,
- *     e.g. the PreNorm Llama configuration B=8, M=2048, Hq=32; not RoCo Falcon at B=2, M=8192, Hq=71);
+ * Same arguments as trinity_attn_block; `workspace` / `workspace_bytes` are ignored.  x_norm (PreNorm with gamma)
+ * is still the caller's.  The call performs no cudaMalloc / cudaFree and calls no allocating routine.  It runs
+ * trinity_attn_block with the array as a workspace of exactly trinity_static_scratch_capacity() bytes, so its
+ * results are bit-identical to that call.  Against a call whose caller lent the full
+ * trinity_attn_block_workspace() they are identical when everything fits; when the optional areas (split-KV
+ * partials, kept scores) fit only in part, fewer splits / the two-pass statistics are used and the results agree
+ * within the rounding of a different summation order.  Limits and rules:
+ *   - only the REQUIRED part of the workspace (fp32 row scales and the two log-sum-exp arrays: B*M*(1+2*Hq)
+ *     values, ~2 M of them fit, e.g. the PreNorm Llama configuration B=8, M=2048, Hq=32) must fit; a problem whose
+ *     required part exceeds the capacity (RoCo Falcon at B=2, M=8192, Hq=71) is refused with
+ *     TRN_E_STATIC_SCRATCH and nothing is launched;
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
  *     device current): make that first call before any stream capture;
  *   - all calls on a device share the one array, which keeps what the previous call left there.  Nothing in
@@ -339,17 +355,6 @@ int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream);
 #define TRN_E_STATIC_SCRATCH (-10) /* problem needs more scratch than the built-in array holds */
 size_t trinity_static_scratch_capacity(void);
 int trinity_attn_block_static(const TrnBlockArgs* a, void* cuda_stream);
-
-/* ------------------------------------------------------------------------------------------------
- * Diagnostic, no reference counterpart: SM clocks per tcgen05.mma (M = 128, K = 16, kind::f16, bf16
- * operands, fp32 accumulation) when one thread issues n_mma of them back to back on every SM, with
- * operands resident on chip.  SS: A and B from shared memory; TS: A from tensor memory (the P v product of
- * the attention kernel).  with_tmem_traffic != 0 adds eight warps that stream tcgen05.ld / st over other
- * tensor-memory columns, as softmax warps do.  Synchronous; allocates 8 bytes for the result.  These are
- * the per-instruction ceilings the GEMM (SS N256) and attention (SS N128, TS N128 / N64) kernels run under.
- * ---------------------------------------------------------------------------------------------- */
-enum { TRN_MMA_SS_N64 = 0, TRN_MMA_SS_N128 = 1, TRN_MMA_SS_N256 = 2, TRN_MMA_TS_N128 = 3, TRN_MMA_TS_N64 = 4 };
-int trinity_probe_mma_rate(int shape, int with_tmem_traffic, int n_mma, double* clocks_per_mma);
 
 #ifdef __cplusplus
 }

@@ -49,5 +49,7 @@ def generate(ref_dir: str, out_dir: str) -> int:
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TRINITY_REFERENCE_DIR")
+    if not ref:
+        sys.exit("usage: python " + sys.argv[0] + " <reference checkout>   (or set TRINITY_REFERENCE_DIR)")
     print(generate(ref, os.path.join(HERE, "_ref")), "modules written to oracle/_ref/")

@@ -82,7 +82,9 @@ def sample_indices(numel: int, n: int = 512) -> np.ndarray:
 
 
 def main() -> None:
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_dir = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TRINITY_REFERENCE_DIR")
+    if not ref_dir:
+        sys.exit("usage: python " + sys.argv[0] + " <reference checkout>   (or set TRINITY_REFERENCE_DIR)")
     ref = import_reference(ref_dir)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
 

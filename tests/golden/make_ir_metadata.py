@@ -24,7 +24,9 @@ def tree(node):
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_dir = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TRINITY_REFERENCE_DIR")
+    if not ref_dir:
+        sys.exit("usage: python " + sys.argv[0] + " <reference checkout>   (or set TRINITY_REFERENCE_DIR)")
     sys.path.insert(0, ref_dir)
     from IrParser import IRParser          # the reference's
     from TritonGen import TritonCodeGen    # the reference's

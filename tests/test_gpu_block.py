@@ -248,6 +248,33 @@ def test_fp32_vanilla_configuration():
     assert_parity(T["K_cache"], r["k_all"][0], "fp32 vanilla k", rel_floor=REL_FLOOR_FP32, rel_tol=REL_TOL_E2E)
 
 
+def test_fp32_caller_keeps_the_cached_prefix_bit_for_bit():
+    """fp32 tensors with P > 0 cached keys: the operator appends rows [P, P+M) of K_cache / V_cache and must leave
+    rows [0, P) exactly as the caller stored them (the reference's kernels store only the appended rows) — also
+    when the kernels work on 16-bit shadows of the caller's fp32 tensors."""
+    consts = {"M": 16, "N": 256, "D": 64, "H": 4, "P": 48}
+    mod = _load_generated(convert_ir_to_triton(open(IR_DIR / "vanilla.txt").read(), SHAPE_DICT, consts), "gen_fp32_prefix")
+    torch.manual_seed(3)
+    host = {"X": torch.randn(16, 256) * 0.3, "WQ": torch.randn(256, 256) / 16, "WK": torch.randn(256, 256) / 16,
+            "WV": torch.randn(256, 256) / 16, "K_cache": torch.randn(4, 64, 64), "V_cache": torch.randn(4, 64, 64),
+            "Q": torch.zeros(4, 16, 64), "O2": torch.zeros(16, 256)}
+    T = {k: v.cuda() for k, v in host.items()}
+    for _ in range(2):
+        mod.forward(*[T[p] for p in mod.TENSOR_PARAMS])
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    for name in ("K_cache", "V_cache"):
+        assert torch.equal(T[name][:, :48].cpu(), host[name][:, :48]), f"{name} prefix was rewritten"
+        assert not torch.equal(T[name][:, 48:].cpu(), host[name][:, 48:])
+    r = O.attn_block("vanilla", X=host["X"], Wq=host["WQ"], Wk=host["WK"], Wv=host["WV"],
+                     cache_K=host["K_cache"].unsqueeze(0), cache_V=host["V_cache"].unsqueeze(0), B=1, M=16, P=48,
+                     Hq=4, Hkv=4, D=64)
+    assert_parity(T["K_cache"][:, 48:], r["k_all"][0, :, 48:], "fp32 cache append", rel_floor=REL_FLOOR_FP32,
+                  rel_tol=REL_TOL_E2E)
+    assert_parity(T["O2"].view(16, 4, 64), r["out_bmhd"][0], "fp32 out with prefix", rel_floor=REL_FLOOR_FP32,
+                  rel_tol=REL_TOL_E2E)
+
+
 @pytest.mark.parametrize("variant,B,stats", (("prenorm", 4, False), ("roco", 3, True), ("keyformer", 9, True)))
 def test_host_activation_path_pipelines_batch_items_with_identical_results(variant, B, stats):
     """trinity_attn_block_host copies batch items in and out while others compute; every output element

@@ -294,17 +294,6 @@ def test_topk_edge_cases():
         ops.topk_keys(odd, 2000)
 
 
-def test_mma_rate_probe_reports_plausible_clocks():
-    from triton_b200 import mma_rate
-    rows = {r["shape"]: r for r in mma_rate.measure(n_mma=1024)}
-    assert L.kernel_status() == 0
-    for r in rows.values():
-        assert 30.0 < r["clk_per_mma"] < 1000.0
-    # twice the columns never cost less than half as much again per instruction
-    assert rows["SS N256"]["clk_per_mma"] >= rows["SS N128"]["clk_per_mma"]
-    assert rows["SS N256"]["mac_per_clk_per_sm"] <= 4096 * 1.05     # the nominal dense bf16 rate per SM
-
-
 @pytest.mark.parametrize("B,M,P,Hq,Hkv,D,dt,causal,noise_mode", (
     (1, 16, 1024, 8, 8, 128, HF, False, L.TRN_NOISE_TENSOR),      # the reference's shape (split-KV with a workspace)
     (2, 200, 72, 6, 2, 64, BF, True, L.TRN_NOISE_GUMBEL),
@@ -388,3 +377,37 @@ def test_lora_linear_layer(M, N, P, R, dt):
     assert torch.equal(o2, o)
     with pytest.raises(L.TrinityError, match="shape"):
         ops.lora(x.cuda(), w.cuda()[:, :P - 8].contiguous(), a.cuda(), b.cuda()[:, :P - 8].contiguous())
+
+
+def test_wait_that_runs_out_is_reported_and_leaves_the_context_usable():
+    """The device-side failure path all kernels share: a bounded wait on a barrier nothing arrives at gives up
+    after its limit, the kernel returns normally (tensor memory freed, no trap), the status word holds the code,
+    later kernels of the library return at once while it is set, and after trinity_clear_kernel_status() the
+    library works as before."""
+    import ctypes as C
+    lib = L.load()
+    assert L.kernel_status() == 0
+    x = torch.randn(64, 256, device="cuda").to(BF)
+    want = ops.rmsnorm(x, None, 1e-5).clone()
+    L.check(lib.trinity_selftest_wait_timeout(1000, None))          # 1 ms
+    st = C.c_int(0)
+    assert lib.trinity_last_kernel_status(C.byref(st)) == -9           # TRN_E_KERNEL
+    assert st.value == 103                                             # KST_TIMEOUT_CONSUMER
+    with pytest.raises(L.TrinityError, match="bounded wait"):
+        L.check(-9)
+    # sticky until cleared; tensor-core kernels launched meanwhile return without touching their outputs
+    assert L.kernel_status() == 103
+    q = torch.randn(1, 128, 2, 64, device="cuda").to(BF)
+    kv = torch.randn(1, 128, 2, 64, device="cuda").to(BF)
+    o = torch.full_like(q, 7.0)
+    ops.attention(q, kv, kv, o, P=0, causal=True, scale=0.125)
+    torch.cuda.synchronize()
+    assert torch.equal(o, torch.full_like(q, 7.0))
+    L.check(lib.trinity_clear_kernel_status())
+    assert L.kernel_status() == 0
+    ops.attention(q, kv, kv, o, P=0, causal=True, scale=0.125)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0 and not torch.equal(o, torch.full_like(q, 7.0))
+    assert torch.equal(ops.rmsnorm(x, None, 1e-5), want)
+    with pytest.raises(L.TrinityError, match="shape"):
+        L.check(lib.trinity_selftest_wait_timeout(0, None))

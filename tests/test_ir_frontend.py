@@ -122,3 +122,54 @@ def test_schedule_follows_the_candidates_fusion_structure():
     assert progs["keyformer"].schedule["scores_in_memory"] == ["C_exp_perturb"]
     assert progs["roco"].schedule["scores_in_memory"] == ["C_exp"]
     assert progs["rmsnorm"].schedule["in_memory"] == ["X2"]
+
+
+_V_DIV = ("(store (tensor O) (/ (load (tensor O) (index (elem n) fulltile fulltile)) (bcast (load (tensor C_sum) "
+          "(index (elem n) fulltile)) 2)) (index (elem n) fulltile fulltile))\n")
+
+
+@pytest.mark.parametrize("what,edit,msg", (
+    ("no softmax division", lambda s: s.replace(_V_DIV, ""), "without the division"),
+    ("scores scaled inside exp", lambda s: s.replace("(exp (* (load (input Q)", "(exp (x 2 (* (load (input Q)")
+     .replace("0 2 1)))", "0 2 1))))", 1), "multiplied by 2"),
+    ("K and V swapped", lambda s: s.replace("(load (input V_cache) (index (elem n) (tile p) fulltile))",
+                                            "(load (input K_cache) (index (elem n) (tile p) fulltile))"), "instead of V_cache"),
+    ("cache overwritten, not appended", lambda s: s.replace("(index (elem n) (const_tile P M) fulltile))))",
+                                                            "(index (elem n) fulltile fulltile))))"), "const_tile"),
+    ("k projected with the wrong weight", lambda s: s.replace("(load (input WK)", "(load (input WQ)"), "WK"),
+))
+def test_candidates_whose_arithmetic_differs_are_refused(what, edit, msg):
+    """A candidate that is not the canonical operator must raise (the harness records the error per candidate,
+    vanilla_llama_benchmark.py:329-332) instead of silently getting the canonical operator's result."""
+    bad = edit(read("vanilla"))
+    assert bad != read("vanilla"), what
+    with pytest.raises(ValueError, match=msg):
+        recognise(IRParser().parse(bad), SHAPE_DICT)
+
+
+def test_norms_and_statistics_are_checked_where_they_apply():
+    # QKNorm whose q is stored without the per-head norm
+    q = read("qknorm")
+    i = q.index("(store (tensor Q1) (/ (load (tensor Q1)")
+    j = q.index("(store (output Q_norm)")
+    with pytest.raises(ValueError, match="Q_norm is not the per-head RMS norm"):
+        recognise(IRParser().parse(q[:i] + q[j:]), SHAPE_DICT)
+    # PreNorm that divides by sqrt(X2 / D) instead of sqrt(X2 / N)
+    with pytest.raises(ValueError, match="normalised X"):
+        recognise(IRParser().parse(read("prenorm_fused").replace("(index fulltile)) N))", "(index fulltile)) D))")), SHAPE_DICT)
+    # RoCo whose second statistic is not squared
+    with pytest.raises(ValueError, match="C_out2"):
+        recognise(IRParser().parse(read("roco").replace("(rsum (sqr (/ (load (tensor C_exp)", "(rsum (x 1 (/ (load (tensor C_exp)")),
+                  SHAPE_DICT)
+
+
+def test_keyformer_temperature_comes_from_the_candidate():
+    kf = read("keyformer")
+    prog = recognise(IRParser().parse(kf), SHAPE_DICT)
+    assert prog.schedule["tau"] == pytest.approx(1.5)              # (x 2 ..) / 3
+    assert recognise(IRParser().parse(kf), SHAPE_DICT, {"TAU_E3": 1500}).schedule["tau"] == pytest.approx(1.5)
+    with pytest.raises(ValueError, match="tau"):
+        recognise(IRParser().parse(kf), SHAPE_DICT, {"TAU_E3": 1000})
+    # tau = 1: the perturbed scores enter exp unscaled
+    one = kf.replace("(exp (/ (x 2 (+ (*", "(exp (+ (*").replace("(index (elem n) fulltile (tile p))))) 3))", "(index (elem n) fulltile (tile p)))))")
+    assert recognise(IRParser().parse(one), SHAPE_DICT).schedule["tau"] == pytest.approx(1.0)

@@ -61,6 +61,41 @@ def test_static_scratch_block_matches_workspace_block_twice(first, second):
             assert torch.equal(got, w), f"{name}: static-scratch result differs from the workspace result"
 
 
+def test_static_scratch_call_allocates_nothing_and_uses_optional_areas_as_far_as_they_fit():
+    """A KeyFormer problem whose required scratch is small but whose optional areas (split-KV partials, 16 MiB of
+    kept scores) exceed the 8 MiB array: the call is accepted, runs the schedule that fits, allocates no device
+    memory (free bytes of the device and torch's own counter unchanged across the call), and equals bit for bit
+    trinity_attn_block given a caller workspace of exactly the array's size."""
+    lib = L.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    cap = lib.trinity_static_scratch_capacity()
+    plan, t = _plan("keyformer", 5, 1, 512, 512, 256, 8, 2, 64, torch.bfloat16)
+    assert lib.trinity_attn_block_workspace(C.byref(plan.args)) > cap          # total does not fit ...
+    ws = torch.empty(cap, dtype=torch.uint8, device="cuda")                     # ... the required part does
+    plan.args.workspace, plan.args.workspace_bytes = ws.data_ptr(), cap
+    plan.run()
+    torch.cuda.synchronize()
+    want = _snapshot(t)
+    full_plan, full_t = _plan("keyformer", 5, 1, 512, 512, 256, 8, 2, 64, torch.bfloat16)
+    full_plan.run()                                                             # everything lent: kept scores
+    L.check(lib.trinity_attn_block_static(C.byref(plan.args), stream))          # first static call on this shape
+    torch.cuda.synchronize()
+    for v in (t["o"], t["q"], t["sp"]):
+        v.zero_()
+    torch.cuda.synchronize()
+    free0, alloc0, resv0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    L.check(lib.trinity_attn_block_static(C.byref(plan.args), stream))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0, "device memory was allocated or freed during the call"
+    assert torch.cuda.memory_allocated() == alloc0 and torch.cuda.memory_reserved() == resv0
+    assert L.kernel_status() == 0
+    for name, w in want.items():
+        assert torch.equal(t[name], w), f"{name}: differs from trinity_attn_block with a workspace of the array's size"
+    # the other schedule (scores kept in memory) agrees within the statistics' tolerance
+    assert (t["sp"] - full_t["sp"]).abs().max().item() <= 1e-3 * 32
+    assert (t["o"].float() - full_t["o"].float()).abs().max().item() <= 2e-2
+
+
 def test_static_scratch_rejects_problems_beyond_its_capacity():
     lib = L.load()
     cap = lib.trinity_static_scratch_capacity()

@@ -25,10 +25,11 @@ VARIANTS = {"vanilla": TRN_VANILLA, "prenorm": TRN_PRENORM, "qknorm": TRN_QKNORM
 # every symbol include/trinity_b200.h declares
 EXPORTS = (
     "trinity_abi_version", "trinity_strerror", "trinity_last_cuda_error", "trinity_last_kernel_status",
+    "trinity_clear_kernel_status", "trinity_selftest_wait_timeout",
     "trinity_rmsnorm", "trinity_qkv_project", "trinity_lora", "trinity_attention", "trinity_attention_workspace",
     "trinity_attn_colstats", "trinity_topk",
     "trinity_attn_block_workspace", "trinity_attn_block", "trinity_attn_block_host",
-    "trinity_static_scratch_capacity", "trinity_attn_block_static", "trinity_convert", "trinity_probe_mma_rate",
+    "trinity_static_scratch_capacity", "trinity_attn_block_static", "trinity_convert",
 )
 
 
@@ -158,8 +159,10 @@ def load() -> C.CDLL:
     lib.trinity_attn_block_workspace.argtypes = [C.POINTER(TrnBlockArgs)]
     lib.trinity_attention_workspace.restype = C.c_size_t
     lib.trinity_attention_workspace.argtypes = [C.POINTER(TrnAttnArgs)]
-    lib.trinity_probe_mma_rate.restype = C.c_int
-    lib.trinity_probe_mma_rate.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
+    lib.trinity_clear_kernel_status.restype = C.c_int
+    lib.trinity_clear_kernel_status.argtypes = []
+    lib.trinity_selftest_wait_timeout.restype = C.c_int
+    lib.trinity_selftest_wait_timeout.argtypes = [C.c_int, C.c_void_p]
     lib.trinity_convert.restype = C.c_int
     lib.trinity_convert.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]
     lib.trinity_static_scratch_capacity.restype = C.c_size_t

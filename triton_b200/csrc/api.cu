@@ -155,7 +155,9 @@ BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
   w.score_pitch = (static_cast<size_t>(a.P) + a.M + 31) / 32 * 32;
   const size_t sb = lse * w.score_pitch * sizeof(float);
   const bool stats = (a.variant == TRN_KEYFORMER || a.variant == TRN_ROCO);
-  w.score_bytes = (stats && sb <= kKeepScoresMaxBytes) ? align_up(sb, 256) : 0;
+  // the from-scores statistics kernel puts batch * heads on grid.y: larger problems take the two-pass kernel
+  const bool grid_ok = static_cast<size_t>(a.B) * a.Hq <= 65535;
+  w.score_bytes = (stats && grid_ok && sb <= kKeepScoresMaxBytes) ? align_up(sb, 256) : 0;
   w.total = off + w.score_bytes;
   return w;
 }
@@ -249,6 +251,16 @@ int trinity_last_kernel_status(int* status_out) {
   return v == 0 ? TRN_OK : TRN_E_KERNEL;
 }
 
+int trinity_clear_kernel_status(void) {
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  TRN_CUDA_TRY(cudaDeviceSynchronize());
+  TRN_CUDA_TRY(cudaMemset(ds->status, 0, sizeof(int)));
+  TRN_CUDA_TRY(cudaDeviceSynchronize());
+  return TRN_OK;
+}
+
 int trinity_rmsnorm(const TrnRmsArgs* a, void* cuda_stream) {
   if (a == nullptr) return TRN_E_NULL;
   DeviceState* ds = nullptr;
@@ -336,6 +348,32 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
   if (stats && a->sum_p == nullptr) return TRN_E_NULL;
   if (a->variant == TRN_ROCO && a->sum_p2 == nullptr) return TRN_E_NULL;
   if (a->variant == TRN_KEYFORMER && a->noise_mode == TRN_NOISE_TENSOR && a->noise == nullptr) return TRN_E_NULL;
+  // Everything the later steps would refuse is refused here, before the first launch: a negative return code
+  // means that nothing ran.
+  {
+    if (a->dtype != TRN_BF16 && a->dtype != TRN_FP16) return TRN_E_DTYPE;
+    if (a->D != 64 && a->D != 128) return TRN_E_SHAPE;
+    if (!(a->scale > 0.f)) return TRN_E_SHAPE;
+    if (a->variant == TRN_KEYFORMER) {
+      if (a->noise_mode <= TRN_NOISE_NONE || a->noise_mode > TRN_NOISE_GUMBEL) return TRN_E_VARIANT;
+      if (!(a->tau > 0.f)) return TRN_E_SHAPE;
+    }
+    auto head_ok = [](const TrnHeadTensor& t) {
+      return aligned16(t.ptr) && (t.stride_b & 7) == 0 && (t.stride_s & 7) == 0 && (t.stride_h & 7) == 0;
+    };
+    if (a->q.ptr == nullptr || a->k_cache.ptr == nullptr || a->v_cache.ptr == nullptr || a->o.ptr == nullptr)
+      return TRN_E_NULL;
+    if (!head_ok(a->q) || !head_ok(a->k_cache) || !head_ok(a->v_cache) || !head_ok(a->o)) return TRN_E_ALIGN;
+    if (!a->skip_projection) {
+      if (a->N <= 0 || (a->N & 7) != 0) return TRN_E_SHAPE;
+      if (static_cast<long long>(a->B) * a->M > 0x7fffffffLL) return TRN_E_SHAPE;
+      if (a->x == nullptr || a->wq == nullptr || a->wk == nullptr || a->wv == nullptr) return TRN_E_NULL;
+      if (!aligned16(a->x) || !aligned16(a->wq) || !aligned16(a->wk) || !aligned16(a->wv)) return TRN_E_ALIGN;
+      if (!aligned16(a->gamma_q) || !aligned16(a->gamma_k) || !aligned16(a->pre_gamma) || !aligned16(a->x_norm))
+        return TRN_E_ALIGN;
+      if (a->variant == TRN_PRENORM && a->pre_gamma != nullptr && a->x_norm == nullptr) return TRN_E_NULL;
+    }
+  }
 
   if (!a->skip_projection) {
     if (a->N <= 0) return TRN_E_SHAPE;

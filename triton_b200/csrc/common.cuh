@@ -79,14 +79,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the CTA is aborting (this thread timed out, or another did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int code,
+                                          uint64_t limit_ns = TRN_WAIT_TIMEOUT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*ctl.abort) return false;
-      if (globaltimer_ns() - t0 > TRN_WAIT_TIMEOUT_NS) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *ctl.abort = 1;
         atomicCAS(ctl.status, 0, code);
         return false;

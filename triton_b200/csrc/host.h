@@ -20,8 +20,8 @@ int record_driver_error(CUresult r, const char* where);
     if (_e != cudaSuccess) return ::trn::record_cuda_error(_e, #expr); \
   } while (0)
 
-// Per-device state created on first use (outside stream capture: the first call on a device
-// allocates one int of device memory for the status word).
+// Per-device state created on first use (make that first call outside stream capture: it looks up the
+// address of the status word, a __device__ variable of the library, with cudaGetSymbolAddress).
 struct DeviceState {
   int device = -1;
   int sm_count = 0;

@@ -13,6 +13,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Set, Tuple
 
 from .ir import ASTNode, NodeType
+from .skeleton import check_skeleton
 
 _TENSOR_NODES = (NodeType.INPUT, NodeType.OUTPUT, NodeType.TENSOR)
 _LOOPS = (NodeType.PLOOP, NodeType.SLOOP)
@@ -124,7 +125,11 @@ def _has_op(root: ASTNode, op: NodeType) -> bool:
     return any(n.node_type == op for n in root.walk())
 
 
-def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None) -> Program:
+def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None,
+              const_dict: Optional[Dict[str, int]] = None) -> Program:
+    """Names the operator, then checks that the candidate's arithmetic IS that operator (skeleton.py): a candidate
+    that differs from it (no softmax division, another score scale, a norm applied elsewhere, K and V swapped ...)
+    raises ValueError instead of being given the canonical operator's result."""
     kernels = _flatten_seq(ast)
     accesses: List[Access] = []
     blocks: Set[str] = set()
@@ -147,6 +152,7 @@ def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None) -> Pr
         tensor_params = sorted(_memory_resident(accesses))
         schedule = {"kernels": len(kernels), "in_memory": sorted(n for n in tensor_params if n in ("C", "D", "E")),
                     "x_norm_in_memory": False, "scores_in_memory": []}
+        check_skeleton(ast, "lora", const_dict)
         return Program("lora", tensor_params, sorted(blocks), names, len(kernels), schedule)
     if "noise" in names:
         variant = "keyformer"
@@ -176,6 +182,7 @@ def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None) -> Pr
             raise ValueError("KeyFormer IR must store C_out")
         if variant == "roco" and not {"C_out1", "C_out2"} <= stored:
             raise ValueError("RoCo IR must store C_out1 and C_out2")
+    derived = check_skeleton(ast, variant, const_dict)
     tensor_params = sorted(_memory_resident(accesses))
     declared_io = {a.name for a in accesses if a.kind in (NodeType.INPUT, NodeType.OUTPUT)}
     in_memory = sorted(n for n in tensor_params if n not in declared_io)
@@ -186,4 +193,6 @@ def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None) -> Pr
         "x_norm_in_memory": variant == "prenorm" and "X_norm" in tensor_params,
         "scores_in_memory": sorted(score_like & set(tensor_params)),
     }
+    if "tau" in derived:
+        schedule["tau"] = round(derived["tau"], 9)      # KeyFormer's temperature as the candidate spells it
     return Program(variant, tensor_params, sorted(blocks), names, len(kernels), schedule)

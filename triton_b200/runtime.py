@@ -39,7 +39,8 @@ class BoundOperator:
         self.causal = bool(c.get("CAUSAL", 0))
         self.scale = float(self.D) ** -0.5 if c.get("SCALE_RSQRT_D", 0) else 1.0
         self.eps = c.get("EPS_E6", 0) * 1e-6
-        self.tau = c.get("TAU_E3", 1500) * 1e-3
+        # KeyFormer's temperature: the TAU_E3 constant, else what the IR candidate itself spells, else the reference's 1.5
+        self.tau = c["TAU_E3"] * 1e-3 if "TAU_E3" in c else float(spec.get("schedule", {}).get("tau", 1.5))
         self.noise_mode = L.TRN_NOISE_GUMBEL if c.get("NOISE_GUMBEL", 0) else L.TRN_NOISE_TENSOR
         self.seed = c.get("SEED", 0)
         self.single_p = bool(c.get("SINGLE_P", 0))
@@ -128,9 +129,18 @@ class BoundOperator:
                    for v in tensors]
         pairs_in = tuple((v, sh) for n, v, sh in zip(self.names, tensors, shadows)
                          if v.dtype == torch.float32 and n in self._INPUTS)
-        pairs_out = tuple((sh, v) for n, v, sh in zip(self.names, tensors, shadows)
-                          if v.dtype == torch.float32 and n in self._OUTPUTS)
-        return self._bind(shadows), pairs_in, pairs_out
+        pairs_out = []
+        for n, v, sh in zip(self.names, tensors, shadows):
+            if v.dtype != torch.float32 or n not in self._OUTPUTS:
+                continue
+            if n in ("K_cache", "V_cache"):
+                # the operator appends rows [P, P+M) and must leave the cached prefix as the caller stored it
+                # (the reference's kernels store only those rows): widen just that slice of the shadow back
+                P, M = self.P, self.M
+                pairs_out.append((sh[..., P:P + M, :], v[..., P:P + M, :]))
+            else:
+                pairs_out.append((sh, v))
+        return self._bind(shadows), pairs_in, tuple(pairs_out)
 
     def __call__(self, tensors: Sequence[torch.Tensor]) -> None:
         key = tuple(int(v.data_ptr()) for v in tensors)
@@ -150,4 +160,7 @@ class BoundOperator:
         else:
             plan[1].run()
         for src, dst in pairs_out:
-            ops.convert(src, dst)
+            if src.is_contiguous() and dst.is_contiguous():
+                ops.convert(src, dst)
+            else:
+                dst.copy_(src)          # strided slice of a cache: a widening copy on the current stream
