@@ -56,7 +56,37 @@ def parity_errors(got, ref, rel_floor=REL_FLOOR):
     return d.max().item(), rel
 
 
-def assert_parity(got, ref, what="", abs_tol=ABS_TOL, rel_tol=REL_TOL, rel_floor=REL_FLOOR):
+# Every comparison is also recorded (max abs error, max relative error at the 1e-3 and at the 0.1 floor) and, when
+# GPU tests ran, written as JSON lines to PARITY_LOG at the end of the session: the measured errors behind the
+# pass / fail verdicts.  `config` groups records of one benchmark configuration.
+PARITY_RECORDS = []
+PARITY_LOG = os.environ.get("TRINITY_PARITY_LOG", os.path.join(ROOT, "gpurun_out", "parity_errors.jsonl"))
+
+
+def record(kind, what, config=None, **fields):
+    PARITY_RECORDS.append(dict(kind=kind, what=what, config=config, **fields))
+
+
+def assert_parity(got, ref, what="", abs_tol=ABS_TOL, rel_tol=REL_TOL, rel_floor=REL_FLOOR, config=None):
     a, r = parity_errors(got, ref, rel_floor)
+    if got.is_cuda:
+        _, r3 = parity_errors(got, ref, 1e-3)
+        _, r1 = parity_errors(got, ref, 1e-1)
+        record("parity", what, config, max_abs=a, max_rel_floor_1em3=r3, max_rel_floor_1em1=r1, abs_tol=abs_tol,
+               rel_tol=rel_tol, rel_floor=rel_floor, max_ref=float(ref.detach().abs().max()), n=int(ref.numel()))
+        print(f"[parity] {what}: max abs {a:.3e}, max rel {r3:.3e} above 1e-3*max, {r1:.3e} above 0.1*max")
     assert a <= abs_tol and r <= rel_tol, f"{what}: max abs {a:.3e} (tol {abs_tol}), max rel {r:.3e} (tol {rel_tol})"
     return a, r
+
+
+def pytest_sessionfinish(session, exitstatus):
+    if not PARITY_RECORDS:
+        return
+    import json
+    try:
+        os.makedirs(os.path.dirname(PARITY_LOG), exist_ok=True)
+        with open(PARITY_LOG, "w") as f:
+            for rec in PARITY_RECORDS:
+                f.write(json.dumps(rec) + "\n")
+    except OSError:
+        pass

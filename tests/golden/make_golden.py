@@ -12,6 +12,10 @@ RoCo classes (ref_rms.py:29-280) on seeded inputs and stores
   golden_small.npz   full inputs and outputs at a small shape (M16 N128 D64 P48)
   golden_native.npz  sampled outputs at the reference's native llama / falcon shapes
                      (convert_eval_rms.py:33-60), inputs regenerated from the seed by the test
+  golden_batched.npz the two reference functions that carry a batch dim or a token-major O2:
+                     SimpleBatchAttention (ref_rms.py:1420-1479, B = 2, PreNorm math, output [B, M, N] token-major)
+                     and reference_kernel (convert_eval_rms.py:122-162, the per-head loop; its function text is
+                     executed as it stands — the module around it imports packages that do not exist)
 
 The fixtures are committed; the tests never need the reference checkout.
 """
@@ -72,6 +76,45 @@ def run_reference(ref, name: str, t, M, N, D, P):
     raise ValueError(name)
 
 
+def load_reference_kernel(ref_dir: str):
+    """convert_eval_rms.py cannot be imported (its first lines import a missing `convert_module` and
+    `baseline.inductor`); its function `reference_kernel` is compiled from the file's own text, unmodified."""
+    import ast
+    path = os.path.join(ref_dir, "convert_eval_rms.py")
+    tree = ast.parse(open(path).read(), path)
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "reference_kernel")
+    ns = {"torch": torch}
+    exec(compile(ast.Module([fn], []), path, "exec"), ns)
+    return ns["reference_kernel"]
+
+
+def make_batched(ref, ref_dir: str) -> dict:
+    """B = 2 through SimpleBatchAttention, and each batch item through reference_kernel."""
+    B, M, N, D, P = 2, 16, 128, 64, 48
+    H = N // D
+    torch.manual_seed(7)
+    std = 0.01
+    t = {"X": torch.randn(B, M, N).clamp(-1, 1) * std, "WQ": torch.randn(N, N).clamp(-1, 1) * std,
+         "WK": torch.randn(N, N).clamp(-1, 1) * std, "WV": torch.randn(N, N).clamp(-1, 1) * std,
+         "K_cache": torch.randn(B, H, P + M, D).clamp(-1, 1) * std, "V_cache": torch.randn(B, H, P + M, D).clamp(-1, 1) * std}
+    out = {"dims": np.array([B, M, N, D, H, P]), "seed": np.array([7])}
+    for k, v in t.items():
+        out["in_" + k] = v.numpy()
+    with torch.no_grad():
+        kc, vc = t["K_cache"].clone(), t["V_cache"].clone()
+        o2 = ref.SimpleBatchAttention(B, M, N, D, P, kc, vc, t["WQ"], t["WK"], t["WV"])(t["X"])
+        out["batch_O2"] = o2.numpy()                      # [B, M, N] token-major
+        out["batch_K_cache"] = kc.numpy()                 # rows [P, P+M) appended in place (ref_rms.py:1460-1461)
+        out["batch_V_cache"] = vc.numpy()
+        rk = load_reference_kernel(ref_dir)
+        per_item = []
+        for b in range(B):
+            kcb, vcb = t["K_cache"][b].clone(), t["V_cache"][b].clone()
+            per_item.append(rk(t["X"][b], t["WQ"], t["WK"], t["WV"], kcb, vcb, M, N, D, H, P))
+        out["loop_O2"] = torch.stack(per_item).numpy()    # [B, M, N]
+    return out
+
+
 OUT_NAMES = {"vanilla": ("out",), "prenorm": ("out",), "qknorm": ("out",),
              "keyformer": ("out", "perturb_out"), "roco": ("out", "sum_p", "sum_p2")}
 
@@ -120,6 +163,7 @@ def main() -> None:
                          flat.abs().max().item()])
                     print(model, name, oname, tuple(o.shape), native[f"{model}_{name}_{oname}_stat"])
     np.savez_compressed(os.path.join(HERE, "golden_native.npz"), **native)
+    np.savez_compressed(os.path.join(HERE, "golden_batched.npz"), **make_batched(ref, ref_dir))
     print("written", os.path.join(HERE, "golden_small.npz"), os.path.join(HERE, "golden_native.npz"))
 
 

@@ -131,6 +131,23 @@ def test_block_against_reference_class_outputs(variant):
         assert_parity(got["sum_p2"][0], torch.from_numpy(g["roco_sum_p2"]), "C_out2", rel_floor=REL_FLOOR_FP32, rel_tol=2e-2)
 
 
+def test_batched_block_against_reference_batched_outputs():
+    """B = 2 against the reference's only batched code, SimpleBatchAttention (ref_rms.py:1420-1479; fixture
+    tests/golden/golden_batched.npz): PreNorm math, cache append per batch item, token-major O2[B, M, N]."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden_batched.npz"))
+    B, M, N, D, H, P = (int(v) for v in g["dims"])
+    t = {k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("in_")}
+    tin = dict(X=t["X"].reshape(B * M, N).half(), WQ=t["WQ"].half(), WK=t["WK"].half(), WV=t["WV"].half(),
+               K_cache=t["K_cache"].half(), V_cache=t["V_cache"].half(), pre_gamma=None, gamma_q=None, gamma_k=None,
+               noise=None)
+    got = run_block("prenorm", tin, B=B, M=M, P=P, Hq=H, Hkv=H, D=D, causal=False, scale=1.0)
+    assert_parity(got["out"].reshape(B, M, N), torch.from_numpy(g["batch_O2"]), "batched prenorm vs SimpleBatchAttention",
+                  rel_floor=REL_FLOOR_FP32, rel_tol=REL_TOL_E2E)
+    assert_parity(got["k_cache"][:, :, P:], torch.from_numpy(g["batch_K_cache"])[:, :, P:], "batched cache append",
+                  rel_floor=REL_FLOOR_FP32, rel_tol=REL_TOL_E2E)
+    assert torch.equal(got["k_cache"][:, :, :P].cpu(), tin["K_cache"][:, :, :P])
+
+
 def _load_generated(src, name):
     import tempfile
     with tempfile.NamedTemporaryFile("w", suffix=".py", delete=False) as f:
@@ -243,9 +260,15 @@ def test_fp32_vanilla_configuration():
     assert L.kernel_status() == 0 and T["O2"].dtype == torch.float32
     r = O.attn_block("vanilla", X=host["X"], Wq=host["WQ"], Wk=host["WK"], Wv=host["WV"], B=1, M=512, P=0, Hq=32, Hkv=8,
                      D=128, causal=True, scale=128 ** -0.5)
-    assert_parity(T["O2"].view(512, 32, 128), r["out_bmhd"][0], "fp32 vanilla out", rel_floor=REL_FLOOR_FP32,
-                  rel_tol=REL_TOL_E2E)
-    assert_parity(T["K_cache"], r["k_all"][0], "fp32 vanilla k", rel_floor=REL_FLOOR_FP32, rel_tol=REL_TOL_E2E)
+    cfg = "cfg1 Vanilla Llama fp32"
+    assert_parity(T["O2"].view(512, 32, 128), r["out_bmhd"][0], "fp32 vanilla out (fp32 oracle, fp32 inputs)",
+                  rel_floor=REL_FLOOR_FP32, rel_tol=REL_TOL_E2E, config=cfg)
+    assert_parity(T["K_cache"], r["k_all"][0], "fp32 vanilla k", rel_floor=REL_FLOOR_FP32, rel_tol=REL_TOL_E2E, config=cfg)
+    # the attention core on the q / k / v the block stored (the step in which both sides see the same inputs)
+    strict = O.attend(T["Q"].cpu().unsqueeze(0), T["K_cache"].cpu().unsqueeze(0), T["V_cache"].cpu().unsqueeze(0), P=0,
+                      causal=True, scale=128 ** -0.5)
+    assert_parity(T["O2"].view(512, 32, 128), strict["out"][0].transpose(0, 1), "fp32 vanilla out (attention on stored q/k/v)",
+                  config=cfg)
 
 
 def test_fp32_caller_keeps_the_cached_prefix_bit_for_bit():

@@ -81,3 +81,21 @@ def test_rmsnorm_matches_reference_formula():
     torch.testing.assert_close(O.rmsnorm(x), x * torch.rsqrt(var))   # ref_rms.py:103
     w = torch.randn(96)
     torch.testing.assert_close(O.rmsnorm(x, w, 1e-6), w * (x * torch.rsqrt(var + 1e-6)))   # ref_attn.py:348-350
+
+
+def test_batched_prenorm_and_token_major_output_equal_reference():
+    """The only reference code with a batch dimension and a token-major O2: SimpleBatchAttention
+    (ref_rms.py:1420-1479, B = 2) and the per-head loop reference_kernel (convert_eval_rms.py:122-162).  Pins the
+    oracle's B > 1 path, its cache append and `out_bmhd` (what the generated kernels store into O2[M, N])."""
+    g = np.load(os.path.join(GOLD, "golden_batched.npz"))
+    B, M, N, D, H, P = (int(v) for v in g["dims"])
+    t = {k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("in_")}
+    r = O.attn_block("prenorm", X=t["X"].reshape(B * M, N), Wq=t["WQ"], Wk=t["WK"], Wv=t["WV"], cache_K=t["K_cache"],
+                     cache_V=t["V_cache"], B=B, M=M, P=P, Hq=H, Hkv=H, D=D)
+    got = r["out_bmhd"].reshape(B, M, N)
+    torch.testing.assert_close(got, torch.from_numpy(g["batch_O2"]), rtol=1e-5, atol=1e-8)
+    torch.testing.assert_close(got, torch.from_numpy(g["loop_O2"]), rtol=1e-5, atol=1e-8)
+    # rows [P, P+M) appended, prefix kept (ref_rms.py:1460-1461)
+    torch.testing.assert_close(r["k_all"], torch.from_numpy(g["batch_K_cache"]), rtol=1e-5, atol=1e-9)
+    torch.testing.assert_close(r["v_all"], torch.from_numpy(g["batch_V_cache"]), rtol=1e-5, atol=1e-9)
+    assert torch.equal(r["k_all"][:, :, :P], t["K_cache"][:, :, :P])

@@ -77,13 +77,60 @@ def local_slices(units: Sequence[Unit], group: int) -> List[LocalSlice]:
     return out
 
 
+def query_head_slices(units: Sequence[Tuple[int, int]]) -> List[LocalSlice]:
+    """MQA: a rank's contiguous (b, query head) units grouped by batch; every slice reads the one shared KV head."""
+    out: List[LocalSlice] = []
+    for b, h in units:
+        if out and out[-1].b == b and out[-1].h1 == h:
+            out[-1] = LocalSlice(b, out[-1].h0, h + 1, 0, 1)
+        else:
+            out.append(LocalSlice(b, h, h + 1, 0, 1))
+    return out
+
+
+def rank_slices(B: int, Hq: int, Hkv: int, rank: int, world_size: int) -> List[LocalSlice]:
+    """What rank `rank` computes: (batch, kv group) units for GQA / MHA; (batch, query head) units when all query
+    heads share ONE KV head (MQA), where kv groups alone could not occupy more than B ranks."""
+    if Hkv == 1 and Hq > 1:
+        return query_head_slices(partition_query_heads(B, Hq, world_size)[rank])
+    return local_slices(partition_units(B, Hkv, world_size)[rank], Hq // Hkv)
+
+
+@dataclass
+class Launch:
+    """One call of the block on a rank: batch items [b0, b0 + nb) with query heads [h0, h1) and kv heads [kv0, kv1).
+    The rank binds only the X rows of those batch items, the WQ columns [h0*D, h1*D), the WK / WV columns
+    [kv0*D, kv1*D) and the cache heads [kv0, kv1)."""
+    b0: int
+    nb: int
+    h0: int
+    h1: int
+    kv0: int
+    kv1: int
+
+
+def rank_launches(B: int, Hq: int, Hkv: int, rank: int, world_size: int) -> List[Launch]:
+    """rank_slices with consecutive batch items of the same head range merged into one launch."""
+    out: List[Launch] = []
+    for s in rank_slices(B, Hq, Hkv, rank, world_size):
+        last = out[-1] if out else None
+        if last and (last.h0, last.h1, last.kv0, last.kv1) == (s.h0, s.h1, s.kv0, s.kv1) and last.b0 + last.nb == s.b:
+            out[-1] = Launch(last.b0, last.nb + 1, s.h0, s.h1, s.kv0, s.kv1)
+        else:
+            out.append(Launch(s.b, 1, s.h0, s.h1, s.kv0, s.kv1))
+    return out
+
+
+def launch_flop_share(launches: Sequence[Launch], B: int, Hq: int) -> float:
+    """Fraction of the whole problem's (batch, query head) pairs in `launches`."""
+    return sum(l.nb * (l.h1 - l.h0) for l in launches) / float(B * Hq)
+
+
 def run_sharded(compute: Callable[[LocalSlice], Dict[str, torch.Tensor]], B: int, Hq: int, Hkv: int,
                 rank: int, world_size: int) -> List[Tuple[LocalSlice, Dict[str, torch.Tensor]]]:
     """Runs `compute` on this rank's slices.  `compute` receives the slice and returns named outputs
     whose dim 0 is the slice's query heads (e.g. out [h1-h0, M, D], sum_p [h1-h0, L])."""
-    parts = partition_units(B, Hkv, world_size)
-    group = Hq // Hkv
-    return [(s, compute(s)) for s in local_slices(parts[rank], group)]
+    return [(s, compute(s)) for s in rank_slices(B, Hq, Hkv, rank, world_size)]
 
 
 def gather_outputs(local: List[Tuple[LocalSlice, Dict[str, torch.Tensor]]], B: int, Hq: int,
