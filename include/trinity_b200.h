@@ -171,8 +171,8 @@ typedef struct {
   const void* noise;     /* TRN_NOISE_TENSOR: element (b,h,i,j) at noise + b*nb + h*nh + i*ni + j */
   int64_t noise_stride_b, noise_stride_h, noise_stride_i;
   uint64_t seed;
-  int single_p;          /* 0 (default): p is carried as hi + lo 16-bit parts into the P v product;
-                            1: one 16-bit part only (faster, ~8 / 11 mantissa bits of p)            */
+  int single_p;          /* 0 (default): p is carried as hi + lo 16-bit parts into the P v product (~16 mantissa
+                            bits of p); 1: one 16-bit part only (faster; 8 mantissa bits for bf16, 11 for fp16) */
   void* workspace;       /* optional device scratch, 256-byte aligned (NULL: none).  With it, a launch that
                             would fill less than half of the SMs divides each tile's key range among several
                             CTAs (split-KV) and merges their partial results with a second small kernel; the

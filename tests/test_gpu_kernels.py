@@ -411,3 +411,66 @@ def test_wait_that_runs_out_is_reported_and_leaves_the_context_usable():
     assert torch.equal(ops.rmsnorm(x, None, 1e-5), want)
     with pytest.raises(L.TrinityError, match="shape"):
         L.check(lib.trinity_selftest_wait_timeout(0, None))
+
+
+@pytest.mark.parametrize("B,M,P,Hq,Hkv,D,dt,causal,single_p", (
+    (1, 256, 0, 2, 1, 128, BF, True, False),
+    (2, 300, 40, 4, 2, 64, BF, True, False),
+    (1, 130, 24, 4, 4, 128, HF, False, True),
+    (1, 16, 1024, 8, 8, 128, HF, False, False),       # few queries per head: row-replicated tiles + split-KV
+    (3, 1, 700, 8, 2, 64, BF, True, False),           # decode
+))
+def test_keyformer_tau_one_generated_noise(B, M, P, Hq, Hkv, D, dt, causal, single_p):
+    """tau = 1 with generated Gumbel noise (the KeyFormer benchmark configuration): exp(s + g) = exp(s) / E, so the
+    fused pass takes the perturbed weight as the plain weight times 1 / E.  Checked against the oracle
+    (ref_rms.py:172-174 with tau = 1 on the same noise), against the separate perturbed-lse pass, and through the
+    whole block."""
+    from gpu_util import run_block
+    scale, seed = D ** -0.5, 9
+    L_ = P + M
+    q, kc, vc = _attn_inputs(B, M, P, Hq, Hkv, D, dt, seed=33)
+    noise = O.gumbel_noise(seed, B, Hq, M, L_)
+    r = O.attend(q.float().transpose(1, 2), kc.float(), vc.float(), P=P, causal=causal, scale=scale, variant="keyformer",
+                 tau=1.0, noise=noise)
+    qv, kv, vv = ops.as_bshd(q.cuda(), "bshd"), ops.as_bshd(kc.cuda(), "bhsd"), ops.as_bshd(vc.cuda(), "bhsd")
+    kw = dict(P=P, causal=causal, scale=scale)
+    nkw = dict(noise_mode=L.TRN_NOISE_GUMBEL, tau=1.0, seed=seed)
+    lse_sep = torch.zeros(B, Hq, M, device="cuda")
+    ops.attention(qv, kv, vv, None, lse=lse_sep, **kw, **nkw)                      # perturbed lse only
+    for use_ws in (False, True):
+        nb = ops.attention_workspace_bytes(B, M, P, Hq, Hkv, D) if use_ws else 0
+        ws = torch.empty(nb, dtype=torch.uint8, device="cuda").fill_(0xff) if nb else None
+        o = torch.zeros(B, M, Hq, D, device="cuda", dtype=dt)
+        lse, lse2 = torch.zeros(B, Hq, M, device="cuda"), torch.zeros(B, Hq, M, device="cuda")
+        ops.attention(qv, kv, vv, o, lse=lse, lse_pert=lse2, workspace=ws, single_p=single_p, **kw, **nkw)
+        sp = torch.zeros(B, Hq, L_, device="cuda")
+        ops.attn_colstats(qv, kv, lse2, sp, None, **kw, **nkw)
+        torch.cuda.synchronize()
+        assert L.kernel_status() == 0
+        if single_p:
+            assert_parity(o, r["out"].transpose(1, 2), "tau=1 fused out (one 16-bit part of p)", rel_floor=0.1, rel_tol=5e-2)
+        else:
+            assert_parity(o, r["out"].transpose(1, 2), "tau=1 fused out")
+        assert (lse2 - lse_sep).abs().max().item() <= 2e-4                          # base-2 log units
+        want_lse2 = torch.logsumexp(_perturbed_scores(q, kc, noise, P, causal, scale), dim=-1) / math.log(2.0)
+        assert (lse2.cpu() - want_lse2).abs().max().item() <= 1e-3
+        assert_parity(sp, r["sum_p"], "tau=1 sum_p", abs_tol=1e-4 * max(1.0, M / 16), rel_tol=2e-4)
+        assert (sp.sum(-1).cpu() - M).abs().max().item() <= 1e-3 * M
+    # whole block (attention + perturbed lse in one pass, statistics, as trinity_attn_block composes them)
+    t = dict(Q=q, K_cache=kc, V_cache=vc, noise=None)
+    got = run_block("keyformer", t, B=B, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, causal=causal, scale=scale, tau=1.0,
+                    noise_mode=L.TRN_NOISE_GUMBEL, seed=seed, project=False)
+    assert_parity(got["out"], r["out"].transpose(1, 2), "tau=1 block out")
+    assert_parity(got["sum_p"], r["sum_p"], "tau=1 block sum_p", abs_tol=1e-4 * max(1.0, M / 16), rel_tol=2e-4)
+
+
+def _perturbed_scores(q, kc, noise, P, causal, scale):
+    """(scale * q k^T + noise) with the causal mask, [B, Hq, M, L] fp32, natural-log domain."""
+    B, M, Hq, D = q.shape
+    grp = Hq // kc.shape[1]
+    s = torch.matmul(q.float().transpose(1, 2), kc.float().repeat_interleave(grp, dim=1).transpose(-1, -2)) * scale + noise
+    if causal:
+        L_ = kc.shape[2]
+        mask = torch.arange(L_).view(1, L_) > (torch.arange(M).view(M, 1) + P)
+        s = s.masked_fill(mask, float("-inf"))
+    return s

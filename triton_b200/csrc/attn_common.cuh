@@ -100,6 +100,11 @@ __host__ __device__ __forceinline__ uint32_t noise_elem_bits(uint32_t rowhash, u
   x ^= x >> 15;
   return x;
 }
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float lg2_approx(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -97,15 +97,24 @@ struct TileInfo {
 constexpr int kDupRows = 32;
 constexpr int kDup = BQ / kDupRows;
 
-template <typename T, int D, int MODE, bool SPLIT, bool DUP>
+template <typename T, int D, int MODE, int PF, bool DUP>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
   using SM = AttnSmem<D>;
   constexpr int KS = SM::kStages;
-  // MODE 0: attention; 1: perturbed log-sum-exp only; 2: both in one pass; 3: attention that also keeps its scores
+  // PF: how p enters the P v product.  0: two 16-bit parts hi + lo of the io type (~16 mantissa bits of p);
+  // 1: one part of the io type (8 bits for bf16, 11 for fp16).  p and v must have the same 16-bit type: a
+  // kind::f16 product of an fp16 A with a bf16 B is refused by the tensor core (illegal instruction on B200).
+  constexpr bool SPLIT = (PF == 0);
+  using PT = T;
+  // MODE 0: attention; 1: perturbed log-sum-exp only; 2: both in one pass; 3: attention that also keeps its scores;
+  // 4: MODE 2 for generated Gumbel noise at tau = 1, where exp(s + g) = exp(s) / E with E = -ln u: the perturbed
+  //    weight is the plain weight the pass computes anyway times 1 / E (one lg2 and one rcp per score instead of
+  //    two lg2 and a second ex2), and the perturbed sum shares the plain softmax's running maximum
   constexpr bool kHasPV = (MODE != 1);                 // P, v and O exist
-  constexpr bool kPert = (MODE == 1 || MODE == 2);     // perturbed log-sum-exp wanted
+  constexpr bool kPert = (MODE == 1 || MODE == 2);     // perturbed log-sum-exp through its own online state
+  constexpr bool kPertT1 = (MODE == 4);                // perturbed sum as p / E beside the plain row sum
   constexpr bool kDump = (MODE == 3);                  // plain scores written out
   __shared__ int s_skip;
   if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(p.status);
@@ -373,7 +382,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = true;
     uint32_t r[32];
     const uint32_t rowhash =
-        kPert ? noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)),
+        (kPert || kPertT1) ? noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)),
                               static_cast<uint32_t>(q_abs))
               : 0u;
     // state of the perturbed log-sum-exp, and where this row's scores go when they are kept
@@ -621,7 +630,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // m_run is the exponent offset in use: (row max seen at the last rescale) - kPBias.  fp16 has few
       // exponent bits, so its p values are biased up by 2^4 to keep the low-order part of p out of
       // the subnormal range; bf16 needs no bias.
-      constexpr float kPBias = (Io<T>::kFmt == 0) ? 4.0f : 0.0f;
+      constexpr float kPBias = (Io<PT>::kFmt == 0) ? 4.0f : 0.0f;
       const float m_target = mb - kPBias;
       const bool grow = (m_target - m_run) > kRescaleThreshold;   // first block: m_run = -inf -> true
       float alpha = 1.0f;
@@ -642,10 +651,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_st32(o_tmem + c * 32, r);
         }
         l_run *= alpha;
+        if constexpr (kPertT1) l2_run *= alpha;
       }
       // ---- pass 2: p = 2^(s * c - m), row sum, P written over S (hi | lo per 32 score columns).
       //      Arithmetic on pairs of columns uses the packed fp32x2 instructions of sm_100.
       float2 lsum = make_float2(0.f, 0.f);
+      float2 lsum2 = make_float2(0.f, 0.f);            // MODE 4: sum of p / E
       const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
       const float2 neg_m2 = make_float2(-m_run, -m_run);
       const float2 minus1 = make_float2(-1.f, -1.f);
@@ -674,15 +685,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               }
             }
 #pragma unroll
-            for (int i = 0; i < G; ++i) pk[i0 + i] = Io<T>::pack2(pp[i].x, pp[i].y);
+            for (int i = 0; i < G; ++i) pk[i0 + i] = Io<PT>::pack2(pp[i].x, pp[i].y);
 #pragma unroll
             for (int i = 0; i < G; ++i) lsum = __fadd2_rn(lsum, pp[i]);
+            if constexpr (kPertT1) {
+              // 1 / E of the same 16 keys (E = -ln u from the counter-based bits), stage by stage over four pairs
+              // at a time; masked keys have p = 0 and add nothing
+              constexpr int H = 4;
+#pragma unroll
+              for (int h0 = 0; h0 < G; h0 += H) {
+                const uint32_t jb = static_cast<uint32_t>(kv0 + c * 32 + 2 * (i0 + h0)) * 0x85ebca6bu;
+                uint32_t xa[H], xb[H];
+                float2 e2[H];
+#pragma unroll
+                for (int i = 0; i < H; ++i) {
+                  xa[i] = rowhash ^ (jb + static_cast<uint32_t>(2 * i) * 0x85ebca6bu);
+                  xb[i] = rowhash ^ (jb + static_cast<uint32_t>(2 * i + 1) * 0x85ebca6bu);
+                }
+#pragma unroll
+                for (int i = 0; i < H; ++i) { xa[i] ^= xa[i] >> 16; xb[i] ^= xb[i] >> 16; }
+#pragma unroll
+                for (int i = 0; i < H; ++i) { xa[i] *= 0x7feb352du; xb[i] *= 0x7feb352du; }
+#pragma unroll
+                for (int i = 0; i < H; ++i) { xa[i] = (xa[i] ^ (xa[i] >> 15)) >> 9; xb[i] = (xb[i] ^ (xb[i] >> 15)) >> 9; }
+#pragma unroll
+                for (int i = 0; i < H; ++i)
+                  e2[i] = make_float2(lg2_approx(unit_from_23bits(xa[i])), lg2_approx(unit_from_23bits(xb[i])));
+#pragma unroll
+                for (int i = 0; i < H; ++i) {
+                  const float va = unit_from_23bits(xa[i] ^ 0x7fffffu), vb = unit_from_23bits(xb[i] ^ 0x7fffffu);   // 1 - u
+                  const float sa = fmaf(0.5f * va, va, va), sb = fmaf(0.5f * vb, vb, vb);
+                  e2[i].x = (va < kGumbelSeriesBelow) ? sa : -0.6931471805599453f * e2[i].x;
+                  e2[i].y = (vb < kGumbelSeriesBelow) ? sb : -0.6931471805599453f * e2[i].y;
+                }
+#pragma unroll
+                for (int i = 0; i < H; ++i) e2[i] = make_float2(rcp_approx(e2[i].x), rcp_approx(e2[i].y));
+#pragma unroll
+                for (int i = 0; i < H; ++i) lsum2 = __ffma2_rn(pp[h0 + i], e2[i], lsum2);
+              }
+            }
             if constexpr (SPLIT) {
               // p = hi + lo with both parts 16-bit: the P v product keeps ~16 mantissa bits of p
 #pragma unroll
-              for (int i = 0; i < G; ++i) pp[i] = __ffma2_rn(Io<T>::unpack2(pk[i0 + i]), minus1, pp[i]);   // p - hi, exact
+              for (int i = 0; i < G; ++i) pp[i] = __ffma2_rn(Io<PT>::unpack2(pk[i0 + i]), minus1, pp[i]);   // p - hi, exact
 #pragma unroll
-              for (int i = 0; i < G; ++i) pk[16 + i0 + i] = Io<T>::pack2(pp[i].x, pp[i].y);
+              for (int i = 0; i < G; ++i) pk[16 + i0 + i] = Io<PT>::pack2(pp[i].x, pp[i].y);
             }
           }
         };
@@ -739,6 +786,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (masked) pass2(std::true_type{});
       else pass2(std::false_type{});
       l_run += lsum.x + lsum.y;
+      if constexpr (kPertT1) l2_run += lsum2.x + lsum2.y;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_ready(t, 1));
@@ -748,6 +796,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const long long part_row =
         ((static_cast<long long>(split) * p.B + b) * p.Hq + h) * p.M + q_abs;   // row of the partial results
     if constexpr (kPert) pert_flush();
+    if constexpr (kPertT1) m2_run = m_run;                    // p / E sums are relative to the plain offset
+    constexpr bool kTwoLse = (MODE == 2 || MODE == 4);       // a second (perturbed) log-sum-exp is reported
     if (MODE == 1) { m_run = m2_run; l_run = l2_run; }        // MODE 1 reports the perturbed value as its lse
     if constexpr (DUP) {
       // ---- merge the four replicas of this tile inside the CTA.  The k / v stages and the q tiles are free once
@@ -765,7 +815,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         float* xo = reinterpret_cast<float*>(smem_gen + SM::kKVOff) + t * (kDup * D * kDupRows);
         float* xl = reinterpret_cast<float*>(smem_gen + SM::kQOff + t * SM::kTileBytes);     // [2][replica][row]
         const float lse1 = m_run + log2f(l_run);            // -inf when this replica saw no visible key
-        const float lse2v = (MODE == 2) ? m2_run + log2f(l2_run) : 0.f;
+        const float lse2v = kTwoLse ? m2_run + log2f(l2_run) : 0.f;
         if (ok && kHasPV) {
           tc_fence_after();
           const float inv_l = (l_run > 0.f) ? 1.0f / l_run : 0.f;
@@ -779,7 +829,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tc_fence_before();
         }
         xl[quad * kDupRows + lane] = lse1;
-        if (MODE == 2) xl[(kDup + quad) * kDupRows + lane] = lse2v;
+        if (kTwoLse) xl[(kDup + quad) * kDupRows + lane] = lse2v;
         // every warp of the warpgroup gets here (all waits above are bounded): named barrier 1 + t, 128 threads
         asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
         // weights of the four replicas for row `lane`
@@ -821,7 +871,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (ok && out_valid && quad == 0) {
           const float lse_m = mx + log2f(tot);
           float lse2_m = 0.f;
-          if (MODE == 2) {
+          if (kTwoLse) {
             float m2 = -INFINITY, t2 = 0.f;
 #pragma unroll
             for (int rp = 0; rp < kDup; ++rp) m2 = fmaxf(m2, xl[(kDup + rp) * kDupRows + lane]);
@@ -835,17 +885,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const long long li = (static_cast<long long>(b) * p.Hq + h) * p.M + qrow;
           if (split_out) {
             p.part_lse[prow_idx] = lse_m;
-            if (MODE == 2) p.part_lse2[prow_idx] = lse2_m;
+            if (kTwoLse) p.part_lse2[prow_idx] = lse2_m;
           } else {
             if (p.lse != nullptr) p.lse[li] = lse_m;
-            if (MODE == 2) p.lse_pert[li] = lse2_m;
+            if (kTwoLse) p.lse_pert[li] = lse2_m;
           }
         }
       } else if (split_out && tile[t].present && quad == 0 && tile[t].q0 + lane < p.M) {
         // this CTA's key range misses the tile: weight 0 in the merge kernel
         const long long prow_idx = ((static_cast<long long>(split) * p.B + b) * p.Hq + h) * p.M + tile[t].q0 + lane;
         p.part_lse[prow_idx] = -INFINITY;
-        if (MODE == 2) p.part_lse2[prow_idx] = -INFINITY;
+        if (kTwoLse) p.part_lse2[prow_idx] = -INFINITY;
       }
     } else {
     if (ok && kHasPV && n_blocks > 0 && warp_active) {
@@ -886,12 +936,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // a CTA whose key range misses this tile contributes weight 0
       if (ok && tile[t].present && row_valid) {
         p.part_lse[part_row] = (n_blocks > 0) ? m_run + log2f(l_run) : -INFINITY;
-        if (MODE == 2) p.part_lse2[part_row] = (n_blocks > 0) ? m2_run + log2f(l2_run) : -INFINITY;
+        if (kTwoLse) p.part_lse2[part_row] = (n_blocks > 0) ? m2_run + log2f(l2_run) : -INFINITY;
       }
     } else if (ok && n_blocks > 0 && row_valid) {
       const long long li = (static_cast<long long>(b) * p.Hq + h) * p.M + q_abs;
       if (p.lse != nullptr) p.lse[li] = m_run + log2f(l_run);
-      if (MODE == 2) p.lse_pert[li] = m2_run + log2f(l2_run);
+      if (kTwoLse) p.lse_pert[li] = m2_run + log2f(l2_run);
     }
     }   // !DUP
   }
@@ -983,7 +1033,7 @@ size_t split_bytes(int n_splits, long long rows, int D, bool with_o) {
   return o_b + 2 * split_lse_bytes(n_splits, rows);
 }
 
-template <typename T, int D, int MODE, bool SPLIT, bool DUP>
+template <typename T, int D, int MODE, int PF, bool DUP>
 int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   using SM = AttnSmem<D>;
   AttnParams p{};
@@ -1031,7 +1081,7 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
                        ? 1
                        : 0;
   p.status = ds.status;
-  auto kern = attn_fwd_kernel<T, D, MODE, SPLIT, DUP>;
+  auto kern = attn_fwd_kernel<T, D, MODE, PF, DUP>;
   rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
   if (rc != TRN_OK) return rc;
   const long long ctas = rows_of_ctas * p.units;
@@ -1063,38 +1113,47 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
     const long long cgrid = (rows + warps_per_cta - 1) / warps_per_cta;
     attn_combine_kernel<T, D><<<static_cast<int>(cgrid), warps_per_cta * 32, 0, st>>>(
         p.part_o, p.part_lse, static_cast<T*>(a.o.ptr), a.o.stride_b, a.o.stride_s, a.o.stride_h, a.lse,
-        MODE == 2 ? p.part_lse2 : nullptr, a.lse_pert, n_parts, a.B, a.Hq, a.M, ds.status);
+        (MODE == 2 || MODE == 4) ? p.part_lse2 : nullptr, a.lse_pert, n_parts, a.B, a.Hq, a.M, ds.status);
     TRN_CUDA_TRY(cudaGetLastError());
   }
   return TRN_OK;
 }
 
 // few queries per head: the row-replicated variant
-template <typename T, int D, int MODE, bool SPLIT>
+template <typename T, int D, int MODE, int PF>
 int launch_variant(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
-  if constexpr (SPLIT || MODE == 1) {
-    if (a.M <= kDupRows) return launch_inst<T, D, MODE, SPLIT, true>(a, st, ds);
+  if constexpr (PF == 0 || MODE == 1) {
+    if (a.M <= kDupRows) return launch_inst<T, D, MODE, PF, true>(a, st, ds);
   }
-  return launch_inst<T, D, MODE, SPLIT, false>(a, st, ds);
+  return launch_inst<T, D, MODE, PF, false>(a, st, ds);
+}
+
+// single_p of the arguments -> PF of the kernel: 0 hi + lo, otherwise one part of the io type
+template <typename T, int D, int MODE>
+int launch_pf(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
+  if (a.single_p == 0) return launch_variant<T, D, MODE, 0>(a, st, ds);
+  return launch_variant<T, D, MODE, 1>(a, st, ds);
 }
 
 template <typename T>
 int launch_typed(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   const bool pert = a.noise_mode != TRN_NOISE_NONE;
   const bool fused = pert && a.lse_pert != nullptr;     // attention and the perturbed log-sum-exp in one pass
+  // generated Gumbel noise at tau = 1 with no scores to keep: exp(s + g) = exp(s) / E
+  const bool fused_t1 = fused && a.noise_mode == TRN_NOISE_GUMBEL && a.tau == 1.0f && a.scores == nullptr;
   if (a.D == 128) {
-    if (fused) return a.single_p ? launch_variant<T, 128, 2, false>(a, st, ds) : launch_variant<T, 128, 2, true>(a, st, ds);
-    if (pert) return launch_variant<T, 128, 1, false>(a, st, ds);
-    if (a.scores != nullptr)
-      return a.single_p ? launch_variant<T, 128, 3, false>(a, st, ds) : launch_variant<T, 128, 3, true>(a, st, ds);
-    return a.single_p ? launch_variant<T, 128, 0, false>(a, st, ds) : launch_variant<T, 128, 0, true>(a, st, ds);
+    if (fused_t1) return launch_pf<T, 128, 4>(a, st, ds);
+    if (fused) return launch_pf<T, 128, 2>(a, st, ds);
+    if (pert) return launch_variant<T, 128, 1, 1>(a, st, ds);
+    if (a.scores != nullptr) return launch_pf<T, 128, 3>(a, st, ds);
+    return launch_pf<T, 128, 0>(a, st, ds);
   }
   if (a.D == 64) {
-    if (fused) return a.single_p ? launch_variant<T, 64, 2, false>(a, st, ds) : launch_variant<T, 64, 2, true>(a, st, ds);
-    if (pert) return launch_variant<T, 64, 1, false>(a, st, ds);
-    if (a.scores != nullptr)
-      return a.single_p ? launch_variant<T, 64, 3, false>(a, st, ds) : launch_variant<T, 64, 3, true>(a, st, ds);
-    return a.single_p ? launch_variant<T, 64, 0, false>(a, st, ds) : launch_variant<T, 64, 0, true>(a, st, ds);
+    if (fused_t1) return launch_pf<T, 64, 4>(a, st, ds);
+    if (fused) return launch_pf<T, 64, 2>(a, st, ds);
+    if (pert) return launch_variant<T, 64, 1, 1>(a, st, ds);
+    if (a.scores != nullptr) return launch_pf<T, 64, 3>(a, st, ds);
+    return launch_pf<T, 64, 0>(a, st, ds);
   }
   return TRN_E_SHAPE;
 }
@@ -1135,6 +1194,7 @@ int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& d
   if (a.B <= 0 || a.M <= 0 || a.P < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.Hq % a.Hkv != 0) return TRN_E_SHAPE;
   if (a.D != 64 && a.D != 128) return TRN_E_SHAPE;
   if (!(a.scale > 0.f)) return TRN_E_SHAPE;
+  if (a.single_p < 0 || a.single_p > 1) return TRN_E_VARIANT;
   const bool pert = a.noise_mode != TRN_NOISE_NONE;
   if (a.noise_mode < TRN_NOISE_NONE || a.noise_mode > TRN_NOISE_GUMBEL) return TRN_E_VARIANT;
   if (a.q.ptr == nullptr || a.k_cache.ptr == nullptr) return TRN_E_NULL;

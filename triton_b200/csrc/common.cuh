@@ -199,7 +199,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 }
 
 // Instruction descriptor for kind::f16 with fp32 accumulation.
-//   fmt: 0 = fp16 operands, 1 = bf16 operands.  a_mn / b_mn: 1 when that operand is MN-major.
+//   fmt: 0 = fp16 operands, 1 = bf16 operands (A and B must have the same type: the tensor core refuses an fp16 A
+//   with a bf16 B).  a_mn / b_mn: 1 when that operand is MN-major.
 __host__ __device__ constexpr uint32_t make_idesc_f16(int fmt, int a_mn, int b_mn, int m, int n) {
   return (1u << 4)                                   // D format = F32
          | (static_cast<uint32_t>(fmt) << 7)         // A format
