@@ -63,6 +63,9 @@ for _prog in NATIVE_PROGRAMS:
 # ... and the neighbouring LoRA operator on the configurations of lora_benchmark.py:545-548
 for _cfg in ("base", "large"):
     WORKLOADS[f"native_lora_{_cfg}"] = dict(variant="native", program="lora", model=_cfg)
+# ... and the gated MLP of gmlp_benchmark.py:53-74 (SiLU gate)
+for _cfg in ("base", "large"):
+    WORKLOADS[f"native_gmlp_{_cfg}"] = dict(variant="native", program="gmlp", model=_cfg)
 METRIC = "fused attn-block TFLOP/s"
 SEED = 1234
 
@@ -746,7 +749,7 @@ def run_native(args, w):
     from triton_b200.harness import AttnBlockBenchmark, tables_for
     prog, model = w["program"], w["model"]
     SHAPE_DICT, consts = tables_for(prog, model)
-    M, N, P = (consts[k] for k in ("M", "N", "P"))
+    M, N, P = consts["M"], consts["N"], consts.get("P", 0)
     D, H = consts.get("D"), consts.get("H")
     ref_path = os.path.join(ROOT, "oracle", "_ref", f"{prog}_{model}.py")
     base = {"metric": METRIC, "unit": "TFLOP/s", "n_gpus": 1, "higher_is_better": True, "scaling": "weak",
@@ -802,6 +805,8 @@ def run_native(args, w):
     elif prog == "lora":
         R = consts["R"]
         flops = 2 * M * N * P + 2 * M * N * R + 2 * M * R * P
+    elif prog == "gmlp":
+        flops = 4 * M * consts["K"] * N
     else:
         flops = 2 * M * N * 3 * H * D + 4 * H * D * M * (P + M)
     line = dict(base, value=None if err else flops / (ms * 1e-3) / 1e12, steps=100, warmup=10,

@@ -150,6 +150,27 @@ typedef struct {
 int trinity_lora(const TrnLoraArgs* a, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Gated MLP, the neighbouring operator of the reference's gmlp_benchmark.py (tensor table :53-74: X[M,K],
+ * W1, W2 [K,N], temporaries C1, C1_exp, C2 [M,N], O[M,N]; the IR's sigmoid / exp nodes, TritonGen.py:2207, 3069-3071):
+ *   c1 = x @ w1,  c2 = x @ w2   (fp32 accumulation)
+ *   o  = gate(c1) * c2          gate = TRN_GATE_SILU: c1 * sigmoid(c1);  TRN_GATE_SIGMOID: sigmoid(c1)
+ * One kernel: both products of an output tile meet in tensor memory and o is rounded once; c1, c2 are never
+ * stored.  x [M, K], w1 / w2 [K, N], o [M, N] row-major and contiguous; K % 8 == 0, N % 64 == 0 (with at most 16
+ * rows and K % 128 == 0, N % 32 == 0 suffices).
+ * ---------------------------------------------------------------------------------------------- */
+enum { TRN_GATE_SILU = 0, TRN_GATE_SIGMOID = 1 };
+typedef struct {
+  const void* x;
+  const void* w1;
+  const void* w2;
+  void* o;
+  int M, K, N;
+  int dtype;
+  int gate;
+} TrnGmlpArgs;
+int trinity_gmlp(const TrnGmlpArgs* a, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Attention core (ref_rms.py:72-81): for every (b, query head h) with kv head h / (Hq/Hkv)
  *   s = scale * q k^T over keys [0, P+M);  causal: query i sees keys j <= P + i
  *   o = softmax(s) v;  lse (optional) = log-sum-exp of s in base 2:  log2(sum_j 2^(s_ij*log2 e))

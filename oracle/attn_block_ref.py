@@ -263,3 +263,13 @@ def lora(X: torch.Tensor, W: torch.Tensor, A: torch.Tensor, B: torch.Tensor,
     if round_d is not None:
         D = D.to(round_d).float()
     return {"D": D, "O": Xf @ Wf + D @ Bf}
+
+
+def gmlp(X: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor, gate: str = "silu") -> Dict[str, torch.Tensor]:
+    """Gated MLP in fp32 (tensor table gmlp_benchmark.py:53-74; sigmoid as the reference generator lowers it,
+    TritonGen.py:2207-2208, 3069-3071): C1 = X @ W1, C2 = X @ W2, C1_exp = sigmoid(C1),
+    O = (C1 * C1_exp) * C2 (gate "silu") or C1_exp * C2 (gate "sigmoid")."""
+    Xf = X.float()
+    C1, C2 = Xf @ W1.float(), Xf @ W2.float()
+    S = torch.sigmoid(C1)
+    return {"C1": C1, "C2": C2, "C1_exp": S, "O": (C1 * S if gate == "silu" else S) * C2}

@@ -5,7 +5,7 @@ the native_* workloads).
 
     python oracle/make_reference_kernels.py [/path/to/reference]
 
-Writes oracle/_ref/<program>_<model>.py for model in {llama, falcon} (the LoRA program: its configurations {base, large}) (git-ignored: derived from the reference,
+Writes oracle/_ref/<program>_<model>.py for model in {llama, falcon} (the LoRA and gated-MLP programs: their configurations {base, large}) (git-ignored: derived from the reference,
 regenerated wherever the reference checkout is present, never committed).  The IR text is this repository's
 (`triton_b200/ir_programs/`; the reference ships no IR files) with one substitution: the head tile of the
 parallel loops, written symbolically there (`(ploop 0 N D n`), is given as the number the model uses
@@ -21,7 +21,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 sys.path.insert(0, ROOT)
 
-from triton_b200.harness import LORA_CONFIGS, MODEL_CONFIGS, tables_for  # noqa: E402
+from triton_b200.harness import configs_of, tables_for  # noqa: E402
 
 
 def generate(ref_dir: str, out_dir: str) -> int:
@@ -35,7 +35,7 @@ def generate(ref_dir: str, out_dir: str) -> int:
         if not fn.endswith(".txt"):
             continue
         program = fn[:-4]
-        for model in (LORA_CONFIGS if program == "lora" else MODEL_CONFIGS):
+        for model in configs_of(program):
             shapes, consts = tables_for(program, model)
             text = open(os.path.join(ir_dir, fn)).read()
             if "D" in consts:

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
-from triton_b200.harness import tables_for  # noqa: E402
+from triton_b200.harness import configs_of, tables_for  # noqa: E402
 
 
 def tree(node):
@@ -38,7 +38,7 @@ def main():
         name = fn[:-4]
         text = open(os.path.join(ir_dir, fn)).read()
         ast = IRParser().parse(text)
-        shapes, consts = tables_for(name, "base" if name == "lora" else "llama")
+        shapes, consts = tables_for(name, sorted(configs_of(name))[0] if "llama" not in configs_of(name) else "llama")
         code = TritonCodeGen().generate(ast, dict(shapes), dict(consts))
         out[name] = {
             "ast": tree(ast),

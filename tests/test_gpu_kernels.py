@@ -474,3 +474,25 @@ def _perturbed_scores(q, kc, noise, P, causal, scale):
         mask = torch.arange(L_).view(1, L_) > (torch.arange(M).view(M, 1) + P)
         s = s.masked_fill(mask, float("-inf"))
     return s
+
+
+@pytest.mark.parametrize("M,K,N,dt,gate", (
+    (16, 1024, 4096, HF, "silu"), (16, 512, 192, BF, "sigmoid"), (300, 1024, 1024, BF, "silu"),
+    (2048, 512, 640, HF, "silu"), (1, 64, 64, BF, "silu"), (129, 136, 320, BF, "sigmoid"),
+    (16, 2048, 8192, HF, "silu"), (7, 128, 96, BF, "sigmoid"), (16, 1024, 64, BF, "silu"), (13, 384, 160, HF, "silu"),
+))
+def test_gated_mlp(M, K, N, dt, gate):
+    """o = gate(x @ w1) * (x @ w2) (gmlp_benchmark.py:53-74) against the fp32 oracle; both products share one
+    accumulator tile and o is rounded once."""
+    torch.manual_seed(17)
+    x = torch.randn(M, K).to(dt)
+    w1, w2 = (torch.randn(K, N) / K ** 0.5).to(dt), (torch.randn(K, N) / K ** 0.5).to(dt)
+    o = torch.full((M, N), float("nan"), dtype=dt, device="cuda")
+    ops.gmlp(x.cuda(), w1.cuda(), w2.cuda(), o, gate=gate)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    want = O.gmlp(x, w1, w2, gate=gate)["O"]
+    # |o| reaches tens here: the absolute bound scales with the output's 16-bit spacing at its largest value
+    assert_parity(o, want, f"gmlp {gate} M{M} K{K} N{N}", abs_tol=max(2e-2, 2.0 ** -8 * want.abs().max().item()))
+    with pytest.raises(L.TrinityError, match="shape"):
+        ops.gmlp(x.cuda(), w1[:, :N - 8].contiguous().cuda(), w2[:, :N - 8].contiguous().cuda(), None, gate=gate)

@@ -27,7 +27,8 @@ REF_DIR = os.path.join(ROOT, "oracle", "_ref")
 IR_DIR = os.path.join(ROOT, "triton_b200", "ir_programs")
 
 CASES = [(p, "llama") for p in ("vanilla", "prenorm", "prenorm_fused", "qknorm", "keyformer", "roco", "rmsnorm")] + \
-        [("vanilla", "falcon"), ("keyformer", "falcon"), ("lora", "base"), ("lora", "large")]
+        [("vanilla", "falcon"), ("keyformer", "falcon"), ("lora", "base"), ("lora", "large"),
+         ("gmlp", "base"), ("gmlp", "large"), ("gmlp_glu", "base")]
 
 
 def _load(path, name):
@@ -43,6 +44,8 @@ def _outputs(program):
         return ["X_norm"]
     if program == "lora":
         return ["O", "D"]
+    if program.startswith("gmlp"):
+        return ["O"]
     outs = ["O2"]
     if program == "keyformer":
         outs.append("C_out")
@@ -58,7 +61,7 @@ def test_against_the_references_generated_kernels(program, model, tmp_path):
         pytest.skip("oracle/_ref not generated (needs the reference checkout: python oracle/make_reference_kernels.py)")
     pytest.importorskip("triton")
     shapes, consts = tables_for(program, model)
-    M, N, P = (consts[k] for k in ("M", "N", "P"))
+    M, N, P = consts["M"], consts["N"], consts.get("P", 0)
     D, H = consts.get("D"), consts.get("H")
     ref_mod = _load(path, f"refgen_{program}_{model}")
     src = convert_ir_to_triton(open(os.path.join(IR_DIR, f"{program}.txt")).read(), shapes, consts)
@@ -79,7 +82,7 @@ def test_against_the_references_generated_kernels(program, model, tmp_path):
         mod.forward(*[T[p] for p in mod.TENSOR_PARAMS])
         torch.cuda.synchronize()
         res = {n: T[n].float().cpu() for n in names}
-        if program not in ("rmsnorm", "lora"):
+        if program not in ("rmsnorm", "lora") and not program.startswith("gmlp"):
             res["K_new"] = T["K_cache"][:, P:].float().cpu()
         return res
 
@@ -93,6 +96,8 @@ def test_against_the_references_generated_kernels(program, model, tmp_path):
     elif program == "lora":
         r = O.lora(host["X"], host["W"], host["A"], host["B"])
         want = {"O": r["O"], "D": r["D"]}
+    elif program.startswith("gmlp"):
+        want = {"O": O.gmlp(host["X"], host["W1"], host["W2"], gate="sigmoid" if program == "gmlp_glu" else "silu")["O"]}
     else:
         variant = program.split("_")[0]
         r = O.attn_block(variant, X=host["X"], Wq=host["WQ"], Wk=host["WK"], Wv=host["WV"],

@@ -9,7 +9,7 @@ import os
 import pytest
 
 from triton_b200.convert_module import convert_ir_to_triton
-from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT, parse_ir_file, resolve_dim, tables_for
+from triton_b200.harness import MODEL_CONFIGS, SHAPE_DICT, configs_of, parse_ir_file, resolve_dim, tables_for
 from triton_b200.ir import ASTNode, IRParser, NodeType
 from triton_b200.recognise import recognise
 
@@ -23,6 +23,10 @@ def tree(node):
     return [node.node_type.value, node.value, [tree(c) for c in node.children]]
 
 
+def first_model(name):
+    return "llama" if "llama" in configs_of(name) else sorted(configs_of(name))[0]
+
+
 def read(name):
     return open(os.path.join(IR_DIR, name + ".txt")).read()
 
@@ -34,8 +38,8 @@ def test_parser_builds_reference_tree(name):
 
 @pytest.mark.parametrize("name", PROGRAMS)
 def test_recogniser_matches_reference_metadata(name):
-    prog = recognise(IRParser().parse(read(name)), tables_for(name, "base" if name == "lora" else "llama")[0])
-    assert prog.variant == name.split("_")[0]          # prenorm_fused is a second PreNorm candidate
+    prog = recognise(IRParser().parse(read(name)), tables_for(name, first_model(name))[0])
+    assert prog.variant == name.split("_")[0]          # prenorm_fused / gmlp_glu are second candidates of an operator
     assert prog.tensor_params == META[name]["tensor_params"]
     assert prog.block_params == META[name]["block_params"]
     assert prog.n_kernels == META[name]["n_kernels"]
@@ -43,7 +47,7 @@ def test_recogniser_matches_reference_metadata(name):
 
 @pytest.mark.parametrize("name", PROGRAMS)
 def test_generated_module_contract(name):
-    src = convert_ir_to_triton(read(name), *tables_for(name, "base" if name == "lora" else "llama"))
+    src = convert_ir_to_triton(read(name), *tables_for(name, first_model(name)))
     mod = pyast.parse(src)
     assigned = {t.id for n in mod.body if isinstance(n, pyast.Assign) for t in n.targets}
     assert {"TENSOR_PARAMS", "BLOCK_PARAMS"} <= assigned
@@ -173,3 +177,20 @@ def test_keyformer_temperature_comes_from_the_candidate():
     # tau = 1: the perturbed scores enter exp unscaled
     one = kf.replace("(exp (/ (x 2 (+ (*", "(exp (+ (*").replace("(index (elem n) fulltile (tile p))))) 3))", "(index (elem n) fulltile (tile p)))))")
     assert recognise(IRParser().parse(one), SHAPE_DICT).schedule["tau"] == pytest.approx(1.0)
+
+
+def test_gated_mlp_gate_comes_from_the_candidate():
+    from triton_b200.harness import GMLP_SHAPE_DICT
+    silu = recognise(IRParser().parse(read("gmlp")), GMLP_SHAPE_DICT)
+    glu = recognise(IRParser().parse(read("gmlp_glu")), GMLP_SHAPE_DICT)
+    assert silu.variant == glu.variant == "gmlp" and silu.schedule["gate"] == 0 and glu.schedule["gate"] == 1
+    # sigmoid spelled through exp: e / (1 + e)
+    via_exp = read("gmlp_glu").replace("(sigmoid (load (tensor C1) (index fulltile (tile n))))",
+                                       "(/ (exp (load (tensor C1) (index fulltile (tile n)))) (+ 1 (exp (load (tensor C1) (index fulltile (tile n))))))")
+    assert recognise(IRParser().parse(via_exp), GMLP_SHAPE_DICT).schedule["gate"] == 1
+    # the gate applied to the wrong product, and no gate at all
+    with pytest.raises(ValueError, match="neither"):
+        recognise(IRParser().parse(read("gmlp").replace("(sigmoid (load (tensor C1)", "(sigmoid (load (tensor C2)")), GMLP_SHAPE_DICT)
+    with pytest.raises(ValueError, match="neither"):
+        recognise(IRParser().parse(read("gmlp_glu").replace("(sigmoid (load (tensor C1) (index fulltile (tile n))))",
+                                                              "(load (tensor C1) (index fulltile (tile n)))")), GMLP_SHAPE_DICT)

@@ -19,6 +19,7 @@ ABI_VERSION = 2
 TRN_BF16, TRN_FP16 = 0, 1
 TRN_VANILLA, TRN_PRENORM, TRN_QKNORM, TRN_KEYFORMER, TRN_ROCO = range(5)
 TRN_NOISE_NONE, TRN_NOISE_TENSOR, TRN_NOISE_GUMBEL = range(3)
+TRN_GATE_SILU, TRN_GATE_SIGMOID = range(2)
 VARIANTS = {"vanilla": TRN_VANILLA, "prenorm": TRN_PRENORM, "qknorm": TRN_QKNORM,
             "keyformer": TRN_KEYFORMER, "roco": TRN_ROCO}
 
@@ -26,7 +27,7 @@ VARIANTS = {"vanilla": TRN_VANILLA, "prenorm": TRN_PRENORM, "qknorm": TRN_QKNORM
 EXPORTS = (
     "trinity_abi_version", "trinity_strerror", "trinity_last_cuda_error", "trinity_last_kernel_status",
     "trinity_clear_kernel_status", "trinity_selftest_wait_timeout",
-    "trinity_rmsnorm", "trinity_qkv_project", "trinity_lora", "trinity_attention", "trinity_attention_workspace",
+    "trinity_rmsnorm", "trinity_qkv_project", "trinity_lora", "trinity_gmlp", "trinity_attention", "trinity_attention_workspace",
     "trinity_attn_colstats", "trinity_topk",
     "trinity_attn_block_workspace", "trinity_attn_block", "trinity_attn_block_host",
     "trinity_static_scratch_capacity", "trinity_attn_block_static", "trinity_convert",
@@ -59,6 +60,13 @@ class TrnLoraArgs(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("w", C.c_void_p), ("a", C.c_void_p), ("b", C.c_void_p), ("o", C.c_void_p),
         ("d", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("P", C.c_int), ("R", C.c_int), ("dtype", C.c_int),
+    ]
+
+
+class TrnGmlpArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w1", C.c_void_p), ("w2", C.c_void_p), ("o", C.c_void_p),
+        ("M", C.c_int), ("K", C.c_int), ("N", C.c_int), ("dtype", C.c_int), ("gate", C.c_int),
     ]
 
 
@@ -148,7 +156,7 @@ def load() -> C.CDLL:
     lib.trinity_last_cuda_error.restype = C.c_char_p
     lib.trinity_last_kernel_status.restype = C.c_int
     lib.trinity_last_kernel_status.argtypes = [C.POINTER(C.c_int)]
-    for name, typ in (("trinity_rmsnorm", TrnRmsArgs), ("trinity_qkv_project", TrnProjArgs), ("trinity_lora", TrnLoraArgs),
+    for name, typ in (("trinity_rmsnorm", TrnRmsArgs), ("trinity_qkv_project", TrnProjArgs), ("trinity_lora", TrnLoraArgs), ("trinity_gmlp", TrnGmlpArgs),
                       ("trinity_attention", TrnAttnArgs), ("trinity_attn_colstats", TrnColStatsArgs),
                       ("trinity_topk", TrnTopkArgs), ("trinity_attn_block", TrnBlockArgs),
                       ("trinity_attn_block_host", TrnBlockHostArgs), ("trinity_attn_block_static", TrnBlockArgs)):

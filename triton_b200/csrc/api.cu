@@ -285,6 +285,14 @@ int trinity_lora(const TrnLoraArgs* a, void* cuda_stream) {
   return launch_lora(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
 }
 
+int trinity_gmlp(const TrnGmlpArgs* a, void* cuda_stream) {
+  if (a == nullptr) return TRN_E_NULL;
+  DeviceState* ds = nullptr;
+  int rc = get_device_state(&ds);
+  if (rc != TRN_OK) return rc;
+  return launch_gmlp(*a, static_cast<cudaStream_t>(cuda_stream), *ds);
+}
+
 int trinity_attention(const TrnAttnArgs* a, void* cuda_stream) {
   if (a == nullptr) return TRN_E_NULL;
   DeviceState* ds = nullptr;

@@ -48,6 +48,10 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int launch_rmsnorm(const TrnRmsArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_qkv_project(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_lora(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds);
+int launch_gmlp(const TrnGmlpArgs& a, cudaStream_t st, const DeviceState& ds);
+// at most 16 tokens: one latency-oriented launch (gmlp_small.cu); callers validate the arguments first
+bool gmlp_small_applies(const TrnGmlpArgs& a);
+int launch_gmlp_small(const TrnGmlpArgs& a, cudaStream_t st, const DeviceState& ds);
 // at most 16 tokens: one latency-oriented launch (lora_small.cu); callers validate the arguments first
 bool lora_small_applies(const TrnLoraArgs& a);
 int launch_lora_small(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds);

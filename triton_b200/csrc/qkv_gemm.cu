@@ -29,7 +29,10 @@ constexpr int kABytes = BM * BK * 2;          // 16 KiB
 constexpr int kBBlockBytes = BK * 64 * 2;     // one 64-column block of w: 64 rows x 128 B = 8 KiB
 constexpr int kThreads = 192;
 constexpr int kBarBytes = 256;
-constexpr int kGroupM = 8;                    // m-tiles per raster group (L2 reuse of the w columns)
+#ifndef TRN_GEMM_GROUP_M
+#define TRN_GEMM_GROUP_M 8
+#endif
+constexpr int kGroupM = TRN_GEMM_GROUP_M;     // m-tiles per raster group (L2 reuse of the w columns)
 
 // Tile width BN: 256 columns for large problems; 128 when the 256-wide tiling would leave SMs idle (the
 // reference's M = 16 shapes stream ~100 MB of weights through only 48 tiles otherwise).
@@ -63,6 +66,7 @@ struct GemmParams {
   int m_tiles, n_tiles_total, total_tiles;
   float qk_eps;
   int K2;              // KCAT kernels: length of the second contraction phase (0 otherwise)
+  int gate;            // GATED kernels: 0 = c1 * sigmoid(c1), 1 = sigmoid(c1)
   int* status;
 };
 
@@ -87,7 +91,12 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
 // KCAT (LoRA, lora_benchmark.py:41-64: o = x @ w + d @ b with d = x @ a): a single output segment whose
 // accumulator runs over two contraction phases, [x | d] @ [w ; b].  The descriptor slots are reused: tm_w0 = w,
 // tm_w1 = b, tm_w2 = d (an activation like x).  Both products meet in fp32 in tensor memory.
-template <typename T, int BN, bool KCAT>
+//
+// GATED (gated MLP, gmlp_benchmark.py:53-74: o = gate(x @ w1) * (x @ w2)): one output segment whose tile is BN / 2
+// columns wide; the accumulator's first half holds x @ w1 and its second half x @ w2 for the SAME output columns
+// (tm_w0 = w1, tm_w1 = w2, each feeding half of the stage's weight blocks), and the epilogue multiplies them.
+//   FORM 0: plain projection, 1: KCAT, 2: GATED
+template <typename T, int BN, int FORM>
 __global__ void __launch_bounds__(kThreads, 1)
 qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w0,
                 const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2,
@@ -98,6 +107,8 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   __syncthreads();
   if (s_skip != 0) return;
 
+  constexpr bool KCAT = (FORM == 1);
+  constexpr bool GATED = (FORM == 2);
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kStageBytes = Cfg::kStageBytes;
@@ -166,9 +177,18 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
           const uint32_t sb = sa + kABytes;
           mbar_expect_tx(full_bar(stage), kStageBytes);
           tma_load_2d(sa, &tm_x, full_bar(stage), ks * BK, tc.m_tile * BM);
+          if constexpr (GATED) {
+            constexpr int HB = BN / 128;           // 64-column blocks per half
 #pragma unroll
-          for (int c = 0; c < BN / 64; ++c)
-            tma_load_2d(sb + c * kBBlockBytes, tm_w, full_bar(stage), tc.n_tile * BN + c * 64, ks * BK);
+            for (int c = 0; c < HB; ++c) {
+              tma_load_2d(sb + c * kBBlockBytes, &tm_w0, full_bar(stage), tc.n_tile * (BN / 2) + c * 64, ks * BK);
+              tma_load_2d(sb + (HB + c) * kBBlockBytes, &tm_w1, full_bar(stage), tc.n_tile * (BN / 2) + c * 64, ks * BK);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * kBBlockBytes, tm_w, full_bar(stage), tc.n_tile * BN + c * 64, ks * BK);
+          }
         }
         __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -261,6 +281,34 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
                    static_cast<long long>(sg.row_off + s) * sg.stride_s;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
 
+      if constexpr (GATED) {
+        // o = gate(c1) * c2 on 32 columns at a time; gate = c1 * sigmoid(c1) (p.gate == 0) or sigmoid(c1)
+        T* out_cols = out_row + tc.n_tile * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          if (tc.n_tile * (BN / 2) + c * 32 >= sg.n) break;
+          uint32_t r1[32], r2[32];
+          tmem_ld32(t_row + c * 32, r1);
+          tmem_ld32(t_row + BN / 2 + c * 32, r2);
+          tmem_wait_ld();
+          if (valid_row) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float c1 = __uint_as_float(r1[i + j]);
+                const float sg1 = __fdividef(1.0f, 1.0f + __expf(-c1));
+                f[j] = (p.gate == 0 ? c1 * sg1 : sg1) * __uint_as_float(r2[i + j]);
+              }
+              uint4 o;
+              o.x = Io<T>::pack2(f[0], f[1]); o.y = Io<T>::pack2(f[2], f[3]);
+              o.z = Io<T>::pack2(f[4], f[5]); o.w = Io<T>::pack2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(out_cols + c * 32 + i) = o;
+            }
+          }
+        }
+      } else
       for (int hh = 0; hh < heads_per_tile; ++hh) {
         const int col0 = tc.n_tile * BN + hh * p.D;
         if (col0 >= sg.n) break;
@@ -331,10 +379,14 @@ struct KcatOperands {
   int K2;
 };
 
-template <typename T, int BN, bool KCAT>
-int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, const KcatOperands* kc = nullptr) {
+template <typename T, int BN, int FORM>
+int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, const KcatOperands* kc = nullptr,
+                 int gate = 0) {
+  constexpr bool KCAT = (FORM == 1);
+  constexpr bool GATED = (FORM == 2);
   using Cfg = GemmCfg<BN>;
   GemmParams p{};
+  p.gate = gate;
   const int rows = a.B * a.M;
   p.rows = rows;
   p.rows_per_batch = a.M;
@@ -358,13 +410,13 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
     s.stride_s = outs[i]->stride_s;
     s.stride_h = outs[i]->stride_h;
     s.n = heads[i] * a.D;
-    s.n_tiles = (s.n + BN - 1) / BN;
+    s.n_tiles = GATED ? (i == 0 ? (s.n + BN / 2 - 1) / (BN / 2) : 0) : (s.n + BN - 1) / BN;
     s.tile0 = tile0;
     tile0 += s.n_tiles;
     s.row_off = (i == 0) ? 0 : a.P;
     s.norm = (a.qk_norm && i < 2) ? 1 : 0;
     s.gamma = s.norm ? gam[i] : nullptr;
-    if (s.n == 0) {                      // segment not present (single-output forms): placeholder descriptor
+    if (s.n == 0 || (GATED && i == 2)) {  // segment not present (single-output forms): placeholder descriptor
       tm_w[i] = tm_w[0];
       continue;
     }
@@ -404,7 +456,7 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
     if (rc != TRN_OK) return rc;
   }
 
-  auto kern = qkv_gemm_kernel<T, BN, KCAT>;
+  auto kern = qkv_gemm_kernel<T, BN, FORM>;
   {
     int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes, ds.device);
     if (rc != TRN_OK) return rc;
@@ -424,8 +476,8 @@ int launch_typed(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
   // 37.3 us against 49.6 us).
   const long long m_tiles = (static_cast<long long>(a.B) * a.M + BM - 1) / BM;
   const long long n128 = (a.Hq * a.D + 127) / 128 + 2LL * ((a.Hkv * a.D + 127) / 128);
-  if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, false>(a, st, ds);
-  return launch_tiled<T, 256, false>(a, st, ds);
+  if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, 0>(a, st, ds);
+  return launch_tiled<T, 256, 0>(a, st, ds);
 }
 
 bool head_tensor_ok(const TrnHeadTensor& t) {
@@ -460,11 +512,48 @@ int launch_lora_typed(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& 
   const KcatOperands kc{a.d, a.b, a.R};
   const long long m_tiles = (static_cast<long long>(a.M) + BM - 1) / BM;
   const long long n128 = (a.P + 127) / 128;
-  if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, true>(p2, st, ds, &kc);
-  return launch_tiled<T, 256, true>(p2, st, ds, &kc);
+  if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, 1>(p2, st, ds, &kc);
+  return launch_tiled<T, 256, 1>(p2, st, ds, &kc);
+}
+
+// o[M, N] = gate(x[M, K] @ w1[K, N]) * (x @ w2[K, N]): one launch; outputs addressed as "heads" of 64 columns.
+// The second weight rides in the k slot: its segment has the same column count, but GATED kernels tile segment 0 only.
+template <typename T>
+int launch_gmlp_typed(const TrnGmlpArgs& a, cudaStream_t st, const DeviceState& ds) {
+  TrnProjArgs pj{};
+  pj.x = a.x;
+  pj.wq = a.w1; pj.wk = a.w2; pj.wv = a.w1;
+  pj.B = 1; pj.M = a.M; pj.P = 0; pj.N = a.K;
+  pj.Hq = a.N / 64; pj.Hkv = a.N / 64; pj.D = 64;
+  pj.dtype = a.dtype;
+  pj.q.ptr = a.o;
+  pj.q.stride_b = static_cast<int64_t>(a.M) * a.N;
+  pj.q.stride_s = a.N;
+  pj.q.stride_h = 64;
+  pj.k_cache = pj.q;
+  pj.v_cache = pj.q;
+  const long long m_tiles = (static_cast<long long>(a.M) + BM - 1) / BM;
+  const long long n64 = (a.N + 63) / 64;
+  // a single row tile streams the weights once: narrow tiles (64 output columns) put that stream on more SMs
+  if (m_tiles == 1 && n64 <= 2LL * ds.sm_count) return launch_tiled<T, 128, 2>(pj, st, ds, nullptr, a.gate);
+  return launch_tiled<T, 256, 2>(pj, st, ds, nullptr, a.gate);
 }
 
 }  // namespace
+
+int launch_gmlp(const TrnGmlpArgs& a, cudaStream_t st, const DeviceState& ds) {
+  if (a.x == nullptr || a.w1 == nullptr || a.w2 == nullptr || a.o == nullptr) return TRN_E_NULL;
+  if (a.M <= 0 || a.K <= 0 || a.N <= 0) return TRN_E_SHAPE;
+  if ((a.K & 7) != 0 || (a.N & 31) != 0) return TRN_E_SHAPE;
+  if (!aligned16(a.x) || !aligned16(a.w1) || !aligned16(a.w2) || !aligned16(a.o)) return TRN_E_ALIGN;
+  if (a.gate != TRN_GATE_SILU && a.gate != TRN_GATE_SIGMOID) return TRN_E_VARIANT;
+  if (a.dtype != TRN_BF16 && a.dtype != TRN_FP16) return TRN_E_DTYPE;
+  if (gmlp_small_applies(a)) return launch_gmlp_small(a, st, ds);
+  if ((a.N & 63) != 0) return TRN_E_SHAPE;       // the tensor-memory kernel stores 64-column blocks
+  if (a.dtype == TRN_BF16) return launch_gmlp_typed<__nv_bfloat16>(a, st, ds);
+  if (a.dtype == TRN_FP16) return launch_gmlp_typed<__half>(a, st, ds);
+  return TRN_E_DTYPE;
+}
 
 int launch_lora(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (a.x == nullptr || a.w == nullptr || a.a == nullptr || a.b == nullptr || a.o == nullptr || a.d == nullptr)

@@ -58,7 +58,7 @@ SHAPE_DICT: Dict[str, Tuple[str, ...]] = {
     "Q_norm": ("H", "M", "D"), "K_norm": ("H", "M", "D"),
 }
 # inputs get random values, everything else starts at zero (vanilla_llama_benchmark.py:131-139)
-INPUT_TENSORS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise", "W", "A", "B")
+INPUT_TENSORS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise", "W", "A", "B", "W1", "W2")
 
 # the LoRA harness has a tensor table of its own (lora_benchmark.py:41-64; configurations :545-548)
 LORA_SHAPE_DICT: Dict[str, Tuple[str, ...]] = {
@@ -71,11 +71,34 @@ LORA_CONFIGS = {
 }
 
 
+# ... and so has the gated-MLP harness (gmlp_benchmark.py:53-74; constants M, N, K, :46-48; its tensor-config file is
+# not part of the reference: two configurations in the spirit of the LoRA ones stand in)
+GMLP_SHAPE_DICT: Dict[str, Tuple[str, ...]] = {
+    "X": ("M", "K"), "W1": ("K", "N"), "W2": ("K", "N"), "O": ("M", "N"),
+    "C1": ("M", "N"), "C2": ("M", "N"), "C1_exp": ("M", "N"),
+}
+GMLP_CONFIGS = {
+    "base": {"M": 16, "N": 4096, "K": 1024},
+    "large": {"M": 16, "N": 8192, "K": 2048},
+}
+
+
+def configs_of(program: str) -> Dict[str, Dict[str, int]]:
+    """The named configurations a packaged program is run on."""
+    if program == "lora":
+        return LORA_CONFIGS
+    if program.startswith("gmlp"):
+        return GMLP_CONFIGS
+    return MODEL_CONFIGS
+
+
 def tables_for(program: str, model: str):
     """(shape table, constants) a packaged program is run with: the attention programs on a model's shape, the LoRA
     program on one of its own configurations."""
     if program == "lora":
         return LORA_SHAPE_DICT, LORA_CONFIGS[model]
+    if program.startswith("gmlp"):
+        return GMLP_SHAPE_DICT, GMLP_CONFIGS[model]
     return SHAPE_DICT, MODEL_CONFIGS[model]
 
 
@@ -130,7 +153,8 @@ class AttnBlockBenchmark:
             torch.manual_seed(self.seed)
         for name in names:
             shape = tuple(resolve_dim(s, self.const_dict) for s in self.shape_dict[name])
-            if name == "noise":
+            if name == "noise" or (name in INPUT_TENSORS and "W1" in self.shape_dict):
+                # noise, and every input of the gated-MLP harness, are plain randn (gmlp_benchmark.py:98-99)
                 t = torch.randn(shape, dtype=self.dtype, device=self.device)
             elif name in INPUT_TENSORS:
                 t = torch.randn(shape, dtype=self.dtype, device=self.device).clamp(-1, 1) * 0.01
@@ -196,15 +220,14 @@ class AttnBlockBenchmark:
         except Exception as e:  # recorded, not raised: the sweep goes on (vanilla_llama_benchmark.py:329-332)
             return BenchmarkResult(ir_id, ir_expr, float("inf"), self.tensor_config, str(e))
 
-    def run_all_benchmarks(self, ir_file: str, start: Optional[int] = None, num: Optional[int] = None,
-                           end: Optional[int] = None) -> List[BenchmarkResult]:
+    def run_all_benchmarks(self, ir_file: str, start: Optional[int] = None,
+                           num: Optional[int] = None) -> List[BenchmarkResult]:
+        """Candidates with id >= start, at most `num` of them (None: all) — vanilla_llama_benchmark.py:334-348."""
         exprs = parse_ir_file(ir_file)
         if start is not None:
             exprs = [e for e in exprs if e[0] >= start]
-        if end is not None:
-            exprs = [e for e in exprs if e[0] <= end]
-        if num:
-            exprs = exprs[:num]
+            if num:
+                exprs = exprs[:num]
         return [self.run_single_benchmark(i, e) for i, e in exprs]
 
     def cleanup(self) -> None:
@@ -218,9 +241,19 @@ class AttnBlockBenchmark:
 
 
 def results_to_json(results: List[BenchmarkResult]) -> List[Dict]:
-    return [{"ir_id": r.ir_id, "ir_expression": r.ir_expression,
-             "execution_time_ms": r.execution_time if math.isfinite(r.execution_time) else None,
+    """The reference's record (vanilla_llama_benchmark.py:390-398, 536-542); a failed candidate keeps
+    execution_time_ms = inf, which json writes as Infinity exactly as the reference's files have it."""
+    return [{"ir_id": r.ir_id, "ir_expression": r.ir_expression, "execution_time_ms": r.execution_time,
              "tensor_config": r.tensor_config, "error": r.error} for r in results]
+
+
+def save_incremental_results(results: List[BenchmarkResult], output_file: str) -> None:
+    """Appends one configuration's records to the output file (vanilla_llama_benchmark.py:517-547)."""
+    try:
+        existing = json.loads(Path(output_file).read_text())
+    except (OSError, ValueError):
+        existing = []
+    Path(output_file).write_text(json.dumps(existing + results_to_json(results), indent=2))
 
 
 def find_best_kernels(results: List[BenchmarkResult], top_k: int = 10) -> List[BenchmarkResult]:
@@ -228,37 +261,73 @@ def find_best_kernels(results: List[BenchmarkResult], top_k: int = 10) -> List[B
     return sorted(ok, key=lambda r: r.execution_time)[:top_k]
 
 
+def write_evaluation_tree(root: str) -> List[str]:
+    """Writes the input files the reference's own *_benchmark.py scripts read, so that they run unmodified against
+    this package's convert_module: ./evaluation/<variant>/<variant>_<model>_cost6_kern2.txt (one `id: (expr)` line per
+    candidate, vanilla_llama_benchmark.py:141-161, 729) and ./evaluation/<model>_configs.json (:731, 743-744).  The
+    reference ships neither (both are git-ignored there); the candidates are this package's IR programs."""
+    written = []
+    ev = Path(root) / "evaluation"
+    for variant in VARIANTS:
+        text = (IR_DIR / f"{variant}.txt").read_text()
+        one_line = " ".join(line.split(";", 1)[0].strip() for line in text.splitlines()).strip()
+        one_line = " ".join(one_line.split())
+        for model in MODEL_CONFIGS:
+            d = ev / variant
+            d.mkdir(parents=True, exist_ok=True)
+            f = d / f"{variant}_{model}_cost6_kern2.txt"
+            f.write_text(f"0: {one_line}\n")
+            written.append(str(f))
+    for model, cfg in MODEL_CONFIGS.items():
+        f = ev / f"{model}_configs.json"
+        f.write_text(json.dumps([cfg], indent=2))
+        written.append(str(f))
+    return written
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="Benchmark IR candidates of one attention-block variant (or the LoRA layer)")
-    ap.add_argument("--variant", choices=VARIANTS + ("prenorm_fused", "lora"), default="vanilla")
-    ap.add_argument("--model", choices=sorted(MODEL_CONFIGS) + sorted(LORA_CONFIGS), default=None,
+    ap.add_argument("--variant", choices=VARIANTS + ("prenorm_fused", "lora", "gmlp", "gmlp_glu"), default="vanilla")
+    ap.add_argument("--model", choices=sorted(set(MODEL_CONFIGS) | set(LORA_CONFIGS) | set(GMLP_CONFIGS)), default=None,
                     help="llama / falcon for the attention programs (default llama); base / large for lora (default base)")
     ap.add_argument("--ir", type=str, default=None, help="IR candidates file (default: the packaged program)")
     ap.add_argument("--tensors", type=str, default=None, help="JSON list of {M,N,D,H,P} (default: the model's)")
     ap.add_argument("--output", type=str, default=None)
-    ap.add_argument("--start", type=int, default=None)
-    ap.add_argument("--num", type=int, default=None)
-    ap.add_argument("--end", type=int, default=None)
-    ap.add_argument("--topk", type=int, default=10)
-    ap.add_argument("--all", action="store_true", help="print every result, not only the top-k")
+    ap.add_argument("--write-evaluation", type=str, default=None, metavar="DIR",
+                    help="write DIR/evaluation/... (IR candidate files and tensor-config JSONs) for the reference's own "
+                         "*_benchmark.py scripts and exit")
+    # the reference's flags (vanilla_llama_benchmark.py:746-753)
+    ap.add_argument("--start", type=int, default=0, help="start from candidate id")
+    ap.add_argument("--num", type=int, default=10, help="number of candidates to benchmark")
+    ap.add_argument("--end", action="store_true", help="run from the start id to the last candidate")
+    ap.add_argument("--topk", type=int, default=5, help="number of best kernels to report")
+    ap.add_argument("--all", action="store_true", help="run every candidate of the file")
     args = ap.parse_args(argv)
+    if args.write_evaluation:
+        for f in write_evaluation_tree(args.write_evaluation):
+            print(f)
+        return 0
+    if args.end and args.num != 10:
+        print("Error: Cannot use --end and --num together. Use either --num or --end, not both.")
+        return 1
 
     ir_file = args.ir or str(IR_DIR / f"{args.variant}.txt")
-    model = args.model or ("base" if args.variant == "lora" else "llama")
+    model = args.model or ("base" if args.variant in ("lora", "gmlp", "gmlp_glu") else "llama")
     shapes, default_cfg = tables_for(args.variant, model)
     configs = json.loads(Path(args.tensors).read_text()) if args.tensors else [default_cfg]
     output = args.output or f"{args.variant}_{model}.json"
-    all_results: List[BenchmarkResult] = []
+    num = None if (args.all or args.end) else args.num
     for cfg in configs:
         bench = AttnBlockBenchmark(cfg, shape_dict=shapes)
-        res = bench.run_all_benchmarks(ir_file, args.start, args.num, args.end)
+        res = bench.run_all_benchmarks(ir_file, args.start, num)
         bench.cleanup()
-        all_results.extend(res)
-        Path(output).write_text(json.dumps(results_to_json(all_results), indent=2))   # incremental
-        shown = res if args.all else find_best_kernels(res, args.topk)
-        for r in shown:
-            state = f"{r.execution_time * 1e3:9.1f} us" if r.error is None else f"error: {r.error}"
-            print(f"config {cfg}  IR {r.ir_id}: {state}")
+        save_incremental_results(res, output)
+        for r in find_best_kernels(res, args.topk):
+            print(f"config {cfg}  IR {r.ir_id}: {r.execution_time * 1e3:9.1f} us")
+        for r in res:
+            if r.error is not None:
+                print(f"config {cfg}  IR {r.ir_id}: error: {r.error}")
+    print(f"All results saved to: {output}")
     return 0
 
 

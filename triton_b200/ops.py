@@ -135,6 +135,27 @@ def lora(x: torch.Tensor, w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, o: 
     return o
 
 
+def gmlp(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, o: Optional[torch.Tensor] = None,
+         gate: str = "silu") -> torch.Tensor:
+    """o = gate(x @ w1) * (x @ w2) (gmlp_benchmark.py:53-74); gate "silu" = c * sigmoid(c), "sigmoid" = sigmoid(c).
+    x [M, K], w1 / w2 [K, N]; one kernel, fp32 accumulation, o rounded once."""
+    _need_cuda(x, w1, w2, o)
+    M, K = x.shape
+    N = w1.shape[1]
+    if w1.shape != (K, N) or w2.shape != (K, N):
+        raise ValueError("gmlp: expected w1, w2 [K, N]")
+    o = torch.empty(M, N, dtype=x.dtype, device=x.device) if o is None else o
+    for t in (x, w1, w2, o):
+        if not t.is_contiguous() or t.dtype != x.dtype:
+            raise ValueError("gmlp: tensors must be contiguous and of one 16-bit dtype")
+    if o.shape != (M, N):
+        raise ValueError("gmlp: o must be [M, N]")
+    code = {"silu": L.TRN_GATE_SILU, "sigmoid": L.TRN_GATE_SIGMOID}[gate]
+    args = L.TrnGmlpArgs(x.data_ptr(), w1.data_ptr(), w2.data_ptr(), o.data_ptr(), M, K, N, _dtype_code(x), code)
+    L.check(L.load().trinity_gmlp(C.byref(args), _stream()))
+    return o
+
+
 def _noise_fields(noise: Optional[torch.Tensor]):
     """noise is a (b, h, i, j) view with contiguous j."""
     if noise is None:

@@ -31,7 +31,7 @@ class Access:
 
 @dataclass
 class Program:
-    variant: str                        # vanilla | prenorm | qknorm | keyformer | roco | rmsnorm
+    variant: str                        # vanilla | prenorm | qknorm | keyformer | roco | rmsnorm | lora | gmlp
     tensor_params: List[str]
     block_params: List[str]
     tensors: Set[str] = field(default_factory=set)
@@ -154,6 +154,13 @@ def recognise(ast: ASTNode, shape_dict: Optional[Dict[str, Tuple]] = None,
                     "x_norm_in_memory": False, "scores_in_memory": []}
         check_skeleton(ast, "lora", const_dict)
         return Program("lora", tensor_params, sorted(blocks), names, len(kernels), schedule)
+    if {"X", "W1", "W2"} <= names and "O" in stored and "K_cache" not in names:
+        # gated MLP (gmlp_benchmark.py:53-74): O = gate(X @ W1) x (X @ W2); the gate is what the candidate spells
+        derived = check_skeleton(ast, "gmlp", const_dict)
+        tensor_params = sorted(_memory_resident(accesses))
+        schedule = {"kernels": len(kernels), "in_memory": sorted(n for n in tensor_params if n in ("C1", "C1_exp", "C2")),
+                    "x_norm_in_memory": False, "scores_in_memory": [], "gate": int(derived["gate"])}
+        return Program("gmlp", tensor_params, sorted(blocks), names, len(kernels), schedule)
     if "noise" in names:
         variant = "keyformer"
     elif {"C_out1", "C_out2"} & names:

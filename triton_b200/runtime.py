@@ -32,6 +32,9 @@ class BoundOperator:
         self._scratch: Dict[str, torch.Tensor] = {}
         if self.variant == "lora":          # constants M, N, P, R (lora_benchmark.py:33-36): nothing else to read
             return
+        if self.variant == "gmlp":          # constants M, N, K (gmlp_benchmark.py:46-48); the gate comes from the IR
+            self.gate = "sigmoid" if spec.get("schedule", {}).get("gate", 0) == 1 else "silu"
+            return
         self.M, self.N, self.D, self.P = c["M"], c["N"], c["D"], c.get("P", 0)
         self.H = c.get("H", self.N // self.D)
         self.B = c.get("B", 1)
@@ -79,6 +82,8 @@ class BoundOperator:
                 d = self._scratch.setdefault("d", torch.empty(t["X"].shape[0], t["A"].shape[1], dtype=t["X"].dtype,
                                                                device=t["X"].device))
             return ("lora", t["X"], t["W"], t["A"], t["B"], t["O"], d)
+        if self.variant == "gmlp":
+            return ("gmlp", t["X"], t["W1"], t["W2"], t["O"])
         if self.variant == "rmsnorm":
             x = t["X"]
             gamma = t.get("gamma")
@@ -115,7 +120,7 @@ class BoundOperator:
             kw.update(sum_p=t["C_out1"], sum_p2=t["C_out2"])
         return ("block", ops.BlockPlan(self.variant, **kw))
 
-    _INPUTS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise", "gamma", "gamma_q", "gamma_k", "W", "A", "B")
+    _INPUTS = ("X", "WQ", "WK", "WV", "K_cache", "V_cache", "noise", "gamma", "gamma_q", "gamma_k", "W", "A", "B", "W1", "W2")
     _OUTPUTS = ("O2", "O1", "O", "Q", "Q_norm", "K_cache", "V_cache", "C_out", "C_out1", "C_out2", "X_norm", "D")
 
     def _bind_any(self, tensors: Sequence[torch.Tensor]):
@@ -154,6 +159,9 @@ class BoundOperator:
         if plan[0] == "lora":
             _, x, w, a, b, o, d = plan
             ops.lora(x, w, a, b, o, d)
+        elif plan[0] == "gmlp":
+            _, x, w1, w2, o = plan
+            ops.gmlp(x, w1, w2, o, gate=self.gate)
         elif plan[0] == "rms":
             _, x, y, gamma, x2 = plan
             ops.rmsnorm(x, gamma, self.eps, out=y)

@@ -285,11 +285,50 @@ class _Checker:
                 _fail("C_out2 is not the sum over queries of the squared attention probabilities")
 
 
+def _check_gmlp(ast: ASTNode) -> Dict[str, float]:
+    """Gated MLP (gmlp_benchmark.py:53-74): O = gate(C1) x C2 with C1 = acc(X * W1), C2 = acc(X * W2) and
+    gate(c) = c x sigmoid(c) (SiLU) or sigmoid(c).  sigmoid may be spelled (sigmoid c) or e / (1 + e) with e = exp(c).
+    Returns {"gate": 0 | 1} (TRN_GATE_SILU | TRN_GATE_SIGMOID)."""
+    flow = Flow()
+    flow.run(ast)
+    o = flow.outputs.get("O")
+    if o is None:
+        _fail("the gated MLP stores no output O")
+
+    def prod(e, w):
+        e = _unacc(e)
+        return e[0] == "*" and _leaf(e[1], "X") and _leaf(e[2], w)
+
+    def sigm(e):
+        if e[0] == "sigmoid" and prod(e[1], "W1"):
+            return True
+        if e[0] == "/" and e[1][0] == "exp" and prod(e[1][1], "W1") and e[2][0] == "+":
+            a, b = e[2][1], e[2][2]
+            return (a == ("const", 1) and b == e[1]) or (b == ("const", 1) and a == e[1])
+        return False
+
+    def factors(e):
+        return factors(e[1]) + factors(e[2]) if e[0] == "x" else [e]
+
+    fs = factors(o)
+    n_c2 = sum(1 for f in fs if prod(f, "W2"))
+    n_sig = sum(1 for f in fs if sigm(f))
+    n_c1 = sum(1 for f in fs if prod(f, "W1"))
+    if n_c2 == 1 and n_sig == 1 and n_c1 == 1 and len(fs) == 3:
+        return {"gate": 0}
+    if n_c2 == 1 and n_sig == 1 and len(fs) == 2:
+        return {"gate": 1}
+    _fail("O is neither (C1 x sigmoid(C1)) x C2 nor sigmoid(C1) x C2 with C1 = X @ W1, C2 = X @ W2")
+    return {}
+
+
 def check_skeleton(ast: ASTNode, variant: str, consts: Optional[Dict[str, int]] = None) -> Dict[str, float]:
     """Raises ValueError unless the candidate's arithmetic is the operator `variant` of this backend.  Returns the
     operator parameters the candidate spells itself (KeyFormer: {"tau": ...})."""
     if variant == "lora":
         return {}       # recognised by its tensor table only (lora_benchmark.py:41-64)
+    if variant == "gmlp":
+        return _check_gmlp(ast)
     flow = Flow()
     flow.run(ast)
     ck = _Checker(flow, variant, consts)
