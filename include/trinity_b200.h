@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define TRINITY_ABI_VERSION 2
+#define TRINITY_ABI_VERSION 3
 
 /* element types of activations / weights / outputs */
 enum { TRN_BF16 = 0, TRN_FP16 = 1 };
@@ -320,6 +320,12 @@ typedef struct {
   int single_p; /* see TrnAttnArgs */
   void* workspace;
   size_t workspace_bytes;
+  int keep_scores; /* KeyFormer / RoCo: where the per-key statistics come from.  0: the library decides by size
+                      (scores kept when [B,Hq,M,P+M] fp32 fit in 32 MiB); 1: keep the scores in the workspace and sum
+                      the statistics from memory whenever they fit in 1 GiB — the schedule of the reference's
+                      candidates that hold C_exp / C_exp_perturb in memory (TritonGen.py:1007-1042); -1: never keep
+                      them, recompute q k^T in a second pass (candidates whose scores live in registers only).
+                      trinity_attn_block_workspace() sizes the workspace for the same choice. */
 } TrnBlockArgs;
 size_t trinity_attn_block_workspace(const TrnBlockArgs* a);
 int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream);

@@ -35,7 +35,8 @@ def test_exports_every_declared_symbol(lib):
 def test_struct_layout_matches_header(tmp_path):
     structs = {"TrnRmsArgs": L.TrnRmsArgs, "TrnHeadTensor": L.TrnHeadTensor, "TrnProjArgs": L.TrnProjArgs,
                "TrnAttnArgs": L.TrnAttnArgs, "TrnColStatsArgs": L.TrnColStatsArgs, "TrnTopkArgs": L.TrnTopkArgs,
-               "TrnBlockArgs": L.TrnBlockArgs, "TrnBlockHostArgs": L.TrnBlockHostArgs, "TrnLoraArgs": L.TrnLoraArgs}
+               "TrnBlockArgs": L.TrnBlockArgs, "TrnBlockHostArgs": L.TrnBlockHostArgs, "TrnLoraArgs": L.TrnLoraArgs,
+               "TrnGmlpArgs": L.TrnGmlpArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
     for sname, st in structs.items():
         lines.append(f'  printf("{sname} %zu\\n", sizeof({sname}));')
@@ -61,7 +62,7 @@ def test_error_codes_and_messages(lib):
         assert lib.trinity_strerror(code).decode() not in ("", "unknown error code")
     assert lib.trinity_strerror(-99).decode() == "unknown error code"
     # NULL argument blocks are refused before any CUDA call
-    for fn in (lib.trinity_rmsnorm, lib.trinity_qkv_project, lib.trinity_lora, lib.trinity_attention, lib.trinity_attn_colstats,
+    for fn in (lib.trinity_rmsnorm, lib.trinity_qkv_project, lib.trinity_lora, lib.trinity_gmlp, lib.trinity_attention, lib.trinity_attn_colstats,
                lib.trinity_topk, lib.trinity_attn_block, lib.trinity_attn_block_host):
         assert fn(None, None) == -1
     assert lib.trinity_attn_block_workspace(None) == 0
@@ -120,3 +121,15 @@ def test_workspace_sizing_policies(lib):
     # large statistics problems recompute q k^T instead of keeping 4 GiB of scores
     big = block_ws("keyformer", 4, 4096, 0, 32, 8, 128)
     assert big == align(4 * 4096 * 4) + 2 * align(4 * 32 * 4096 * 4)
+
+    # keep_scores: the caller (the IR candidate's structure) can ask for either schedule
+    def block_ws_keep(keep, B, M, P):
+        a = L.TrnBlockArgs()
+        a.variant, a.B, a.M, a.P, a.N, a.Hq, a.Hkv, a.D = L.VARIANTS["roco"], B, M, P, 4096, 32, 32, 128
+        a.keep_scores = keep
+        return lib.trinity_attn_block_workspace(C.byref(a))
+    assert block_ws_keep(-1, 1, 16, 1024) == base + split                      # never kept: two-pass statistics
+    assert block_ws_keep(1, 1, 16, 1024) == base + split + scores
+    mid = 1 * 32 * 512 * 1024 * 4                                              # 64 MiB of scores: kept only on request
+    assert block_ws_keep(0, 1, 512, 512) < mid <= block_ws_keep(1, 1, 512, 512)
+    assert block_ws_keep(1, 4, 4096, 0) < (1 << 30)                            # 8 GiB of scores: never

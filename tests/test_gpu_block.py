@@ -373,3 +373,32 @@ def test_prenorm_candidate_that_keeps_x_norm_in_registers_selects_the_fused_sche
     assert_parity(outs["fused"][1], outs["stored"][1].float().cpu(), "fused vs stored schedule", rel_tol=5e-2,
                   rel_floor=0.1)
     assert L.kernel_status() == 0
+
+
+def test_candidate_structure_selects_the_statistics_schedule():
+    """Two RoCo candidates with the same arithmetic: the packaged one keeps C_exp in memory between its two key loops
+    (-> scores kept in the workspace, statistics summed from memory), the second recomputes exp(q k^T) in the
+    statistics loop and holds no score tensor (-> second q k^T pass).  Both give the same operator."""
+    consts = {"M": 16, "N": 256, "D": 64, "H": 4, "P": 48}
+    kept = open(IR_DIR / "roco.txt").read()
+    load_cexp = "(load (tensor C_exp) (index (elem n) fulltile (tile p)))"
+    again = ("(exp (* (load (input Q) (index (elem n) fulltile fulltile)) "
+             "(permute3 (load (input K_cache) (index (elem n) (tile p) fulltile)) 0 2 1)))")
+    head, sep, tail = kept.rpartition("(sloop 0 P+M tile_p p")
+    recompute = head + sep + tail.replace(load_cexp, again)
+    assert recompute != kept
+    outs = {}
+    for name, ir in (("kept", kept), ("recompute", recompute)):
+        mod = _load_generated(convert_ir_to_triton(ir, SHAPE_DICT, consts), f"gen_roco_{name}")
+        bench = AttnBlockBenchmark(consts, seed=42)
+        bench.create_test_tensors(mod.TENSOR_PARAMS)
+        mod.forward(*[bench.tensors[p] for p in mod.TENSOR_PARAMS])
+        torch.cuda.synchronize()
+        outs[name] = (mod, {k: bench.tensors[k].float().cpu() for k in ("O2", "C_out1", "C_out2")})
+    assert outs["kept"][0].SCHEDULE["scores_in_memory"] == ["C_exp"] and "C_exp" in outs["kept"][0].TENSOR_PARAMS
+    assert outs["recompute"][0].SCHEDULE["scores_in_memory"] == [] and "C_exp" not in outs["recompute"][0].TENSOR_PARAMS
+    assert outs["kept"][0]._op.keep_scores == 1 and outs["recompute"][0]._op.keep_scores == -1
+    assert torch.equal(outs["kept"][1]["O2"], outs["recompute"][1]["O2"])
+    for k in ("C_out1", "C_out2"):
+        assert_parity(outs["recompute"][1][k].cuda().half(), outs["kept"][1][k], f"{k}: recompute vs kept scores", rel_tol=2e-2)
+    assert L.kernel_status() == 0

@@ -14,7 +14,7 @@ LIB_NAME = "libtrinity_b200.so"
 # TRINITY_B200_LIB points at another build of the same library (e.g. one compiled with extra -D flags)
 LIB_PATH = Path(os.environ.get("TRINITY_B200_LIB") or (Path(__file__).resolve().parent / LIB_NAME))
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 TRN_BF16, TRN_FP16 = 0, 1
 TRN_VANILLA, TRN_PRENORM, TRN_QKNORM, TRN_KEYFORMER, TRN_ROCO = range(5)
@@ -117,7 +117,7 @@ class TrnBlockArgs(C.Structure):
         ("noise_stride_b", C.c_int64), ("noise_stride_h", C.c_int64), ("noise_stride_i", C.c_int64),
         ("seed", C.c_uint64),
         ("sum_p", C.c_void_p), ("sum_p2", C.c_void_p), ("stats_fp32", C.c_int), ("single_p", C.c_int),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("keep_scores", C.c_int),
     ]
 
 

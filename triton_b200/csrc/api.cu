@@ -135,6 +135,8 @@ struct BlockWorkspace {
 // KeyFormer / RoCo problems whose [B, Hq, M, P+M] fp32 scores fit in this many bytes keep them in memory and sum
 // the per-key statistics from there (one q k^T pass instead of two)
 constexpr size_t kKeepScoresMaxBytes = 32u << 20;
+// ... and up to this size when the caller asks for the kept-scores schedule (TrnBlockArgs.keep_scores = 1)
+constexpr size_t kKeepScoresHardMaxBytes = 1u << 30;
 
 BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
   BlockWorkspace w{};
@@ -157,7 +159,8 @@ BlockWorkspace block_workspace_layout(const TrnBlockArgs& a) {
   const bool stats = (a.variant == TRN_KEYFORMER || a.variant == TRN_ROCO);
   // the from-scores statistics kernel puts batch * heads on grid.y: larger problems take the two-pass kernel
   const bool grid_ok = static_cast<size_t>(a.B) * a.Hq <= 65535;
-  w.score_bytes = (stats && grid_ok && sb <= kKeepScoresMaxBytes) ? align_up(sb, 256) : 0;
+  const bool fits = a.keep_scores > 0 ? sb <= kKeepScoresHardMaxBytes : (a.keep_scores == 0 && sb <= kKeepScoresMaxBytes);
+  w.score_bytes = (stats && grid_ok && fits) ? align_up(sb, 256) : 0;
   w.total = off + w.score_bytes;
   return w;
 }

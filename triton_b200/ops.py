@@ -249,7 +249,7 @@ class BlockPlan:
                  gamma_k: Optional[torch.Tensor] = None,
                  noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
                  seed: int = 0, sum_p: Optional[torch.Tensor] = None, sum_p2: Optional[torch.Tensor] = None,
-                 single_p: bool = False, x_norm: Optional[torch.Tensor] = None):
+                 single_p: bool = False, x_norm: Optional[torch.Tensor] = None, keep_scores: int = 0):
         _need_cuda(q, k_cache, v_cache, o, x, wq, wk, wv, pre_gamma, gamma_q, gamma_k, noise, sum_p, sum_p2, x_norm)
         self.variant = variant
         skip = x is None
@@ -288,6 +288,8 @@ class BlockPlan:
         a.sum_p, a.sum_p2 = _ptr(sum_p), _ptr(sum_p2)
         a.stats_fp32 = int(sum_p is not None and sum_p.dtype == torch.float32)
         a.single_p = int(single_p)
+        # KeyFormer / RoCo statistics: 0 = by size, 1 = from scores kept in the workspace, -1 = second q k^T pass
+        a.keep_scores = int(keep_scores)
         lib = L.load()
         nbytes = lib.trinity_attn_block_workspace(C.byref(a))
         self._ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)

@@ -47,6 +47,9 @@ class BoundOperator:
         self.noise_mode = L.TRN_NOISE_GUMBEL if c.get("NOISE_GUMBEL", 0) else L.TRN_NOISE_TENSOR
         self.seed = c.get("SEED", 0)
         self.single_p = bool(c.get("SINGLE_P", 0))
+        # the candidate's structure picks the statistics schedule: score tensors it holds in memory (C_exp,
+        # C_exp_perturb ...) -> scores kept in the workspace and summed from there; none -> second q k^T pass
+        self.keep_scores = 1 if spec.get("schedule", {}).get("scores_in_memory") else -1
         self._plans: Dict[Tuple[int, ...], object] = {}
         self._scratch: Dict[str, torch.Tensor] = {}
 
@@ -102,7 +105,7 @@ class BoundOperator:
                   o=self._head_view(t[o_name], o_name), x=t["X"].reshape(B * M, self.N), wq=t["WQ"], wk=t["WK"],
                   wv=t["WV"], causal=self.causal, scale=self.scale, pre_eps=self.eps, qk_eps=self.eps,
                   pre_gamma=t.get("gamma"), gamma_q=t.get("gamma_q"), gamma_k=t.get("gamma_k"),
-                  single_p=self.single_p)
+                  single_p=self.single_p, keep_scores=self.keep_scores)
         if self.variant == "prenorm" and "X_norm" in t:
             # the program keeps X_norm in memory (a kernel of its own stores it): same schedule here, and the
             # caller's tensor receives the normalised rows as it would from the generated kernels
