@@ -288,7 +288,9 @@ class LaunchData:
                                   k_cache=ops.as_bshd(self.kc, "bhsd"), v_cache=ops.as_bshd(self.vc, "bhsd"),
                                   o=ops.as_bshd(self.o, "bshd"), causal=True, scale=D ** -0.5,
                                   noise_mode=L.TRN_NOISE_GUMBEL if variant == "keyformer" else 0, tau=1.0, seed=0,
-                                  sum_p=self.sp, sum_p2=self.sp2, **kw)
+                                  sum_p=self.sp, sum_p2=self.sp2,
+                                  # a slice of the whole problem sees the whole problem's generated noise
+                                  noise_heads=Hq, noise_bh0=la.b0 * Hq + la.h0, **kw)
         self.flops = sum(algorithmic_flops(dict(w, B=nb, Hq=nh, Hkv=nkv)))
 
     def step(self):
@@ -306,7 +308,11 @@ class LaunchData:
     def checksum(self, n_heads):
         """float64 sum and sum of magnitudes of the output of the first batch item's first n_heads heads."""
         o = self.o[0, :, :n_heads].double()
-        return [float(o.sum()), float(o.abs().sum())]
+        c = [float(o.sum()), float(o.abs().sum())]
+        if self.sp is not None:                       # per-key statistics of the same heads (KeyFormer: noise included)
+            c[0] += float(self.sp[0, :n_heads].double().sum())
+            c[1] += float(self.sp[0, :n_heads].double().abs().sum())
+        return c
 
 
 def run_ours(args, w):

@@ -208,6 +208,11 @@ typedef struct {
                             statistics from memory instead of a second q k^T pass (the schedule of the
                             reference's programs that keep C_exp / C_exp_perturb in memory)               */
   int64_t score_pitch;   /* elements per (b, h, query) row of `scores`: a multiple of 32, >= P + M */
+  int noise_heads;       /* TRN_NOISE_GUMBEL: the generated field is indexed by (b * noise_heads + h + noise_bh0, i, j).
+                            0 means Hq.  A caller that runs a SLICE of a larger problem (a rank's batch items / heads)
+                            passes the whole problem's head count and the flat index of its first (batch, head), and
+                            gets exactly the noise the unsliced problem would see                              */
+  int noise_bh0;
 } TrnAttnArgs;
 int trinity_attention(const TrnAttnArgs* a, void* cuda_stream);
 /* Scratch that makes split-KV possible for this shape (0: the launch would not split).  No reference
@@ -244,6 +249,8 @@ typedef struct {
                             exist), `lse` must be the
                             log-sum-exp that belongs to those scores                                        */
   int64_t score_pitch;
+  int noise_heads;       /* as in TrnAttnArgs */
+  int noise_bh0;
 } TrnColStatsArgs;
 int trinity_attn_colstats(const TrnColStatsArgs* a, void* cuda_stream);
 
@@ -326,6 +333,8 @@ typedef struct {
                       candidates that hold C_exp / C_exp_perturb in memory (TritonGen.py:1007-1042); -1: never keep
                       them, recompute q k^T in a second pass (candidates whose scores live in registers only).
                       trinity_attn_block_workspace() sizes the workspace for the same choice. */
+  int noise_heads; /* as in TrnAttnArgs: slices of a larger KeyFormer problem see the whole problem's noise */
+  int noise_bh0;
 } TrnBlockArgs;
 size_t trinity_attn_block_workspace(const TrnBlockArgs* a);
 int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream);

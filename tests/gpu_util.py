@@ -32,7 +32,7 @@ def block_inputs(seed, B, M, P, N, Hq, Hkv, D, dt, ref_native=False, variant="va
 
 
 def run_block(variant, t, *, B, M, P, Hq, Hkv, D, causal, scale, eps=0.0, tau=1.5, noise_mode=L.TRN_NOISE_TENSOR,
-              seed=0, stats_dtype=torch.float32, single_p=False, project=True):
+              seed=0, stats_dtype=torch.float32, single_p=False, project=True, noise_heads=0, noise_bh0=0):
     """Returns dict(out [B,M,Hq,D], q, k_cache, v_cache, sum_p, sum_p2) of device tensors."""
     dev = lambda x: None if x is None else x.cuda()
     dt = t["K_cache"].dtype
@@ -50,7 +50,8 @@ def run_block(variant, t, *, B, M, P, Hq, Hkv, D, causal, scale, eps=0.0, tau=1.
     plan = ops.BlockPlan(variant, B=B, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, q=ops.as_bshd(q, "bshd"),
                          k_cache=ops.as_bshd(kc, "bhsd"), v_cache=ops.as_bshd(vc, "bhsd"), o=ops.as_bshd(o, "bshd"),
                          causal=causal, scale=scale, noise_mode=noise_mode if variant == "keyformer" else 0, tau=tau,
-                         noise=dev(t.get("noise")), seed=seed, sum_p=sp, sum_p2=sp2, single_p=single_p, **kw)
+                         noise=dev(t.get("noise")), seed=seed, sum_p=sp, sum_p2=sp2, single_p=single_p,
+                         noise_heads=noise_heads, noise_bh0=noise_bh0, **kw)
     plan.run()
     torch.cuda.synchronize()
     assert L.kernel_status() == 0

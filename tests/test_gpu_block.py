@@ -298,10 +298,13 @@ def test_fp32_caller_keeps_the_cached_prefix_bit_for_bit():
                   rel_tol=REL_TOL_E2E)
 
 
-@pytest.mark.parametrize("variant,B,stats", (("prenorm", 4, False), ("roco", 3, True), ("keyformer", 9, True)))
+@pytest.mark.parametrize("variant,B,stats", (("prenorm", 4, False), ("roco", 3, True), ("keyformer", 9, True),
+                                             ("keyformer_gumbel", 5, True)))
 def test_host_activation_path_pipelines_batch_items_with_identical_results(variant, B, stats):
     """trinity_attn_block_host copies batch items in and out while others compute; every output element
     must equal the one-pass device result bit for bit (odd batch counts: uneven last group)."""
+    gumbel = variant == "keyformer_gumbel"                # generated noise: batch groups must see the uncut problem's
+    variant = variant.split("_")[0]
     M, P, N, Hq, Hkv, D = 512, 64, 1024, 8, 2, 128        # x and o: 1 MB per batch item each
     L_ = P + M
     torch.manual_seed(31)
@@ -309,7 +312,7 @@ def test_host_activation_path_pipelines_batch_items_with_identical_results(varia
     x = torch.randn(B * M, N).to(dt)
     wq, wk, wv = ((torch.randn(N, h * D) / N ** 0.5).to(dt).cuda() for h in (Hq, Hkv, Hkv))
     kc0, vc0 = torch.randn(B, Hkv, L_, D).to(dt), torch.randn(B, Hkv, L_, D).to(dt)
-    noise = torch.randn(B, Hq, M, L_).to(dt).cuda() if variant == "keyformer" else None
+    noise = torch.randn(B, Hq, M, L_).to(dt).cuda() if (variant == "keyformer" and not gumbel) else None
     gamma = (1 + 0.1 * torch.randn(N)).to(dt).cuda() if variant == "prenorm" else None
 
     def make():
@@ -322,8 +325,8 @@ def test_host_activation_path_pipelines_batch_items_with_identical_results(varia
         plan = ops.BlockPlan(variant, B=B, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, q=q, k_cache=ops.as_bshd(kc, "bhsd"),
                              v_cache=ops.as_bshd(vc, "bhsd"), o=o, x=xd, wq=wq, wk=wk, wv=wv, causal=True,
                              scale=D ** -0.5, pre_eps=1e-5, pre_gamma=gamma,
-                             noise_mode=L.TRN_NOISE_TENSOR if variant == "keyformer" else L.TRN_NOISE_NONE, tau=1.5,
-                             noise=noise, sum_p=sp, sum_p2=sp2)
+                             noise_mode=(L.TRN_NOISE_GUMBEL if gumbel else L.TRN_NOISE_TENSOR) if variant == "keyformer"
+                             else L.TRN_NOISE_NONE, tau=1.5, seed=77, noise=noise, sum_p=sp, sum_p2=sp2)
         return plan, xd, o, kc, vc, sp, sp2
 
     plan, xd, o_ref, kc_ref, vc_ref, sp_ref, sp2_ref = make()

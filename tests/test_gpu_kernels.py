@@ -496,3 +496,23 @@ def test_gated_mlp(M, K, N, dt, gate):
     assert_parity(o, want, f"gmlp {gate} M{M} K{K} N{N}", abs_tol=max(2e-2, 2.0 ** -8 * want.abs().max().item()))
     with pytest.raises(L.TrinityError, match="shape"):
         ops.gmlp(x.cuda(), w1[:, :N - 8].contiguous().cuda(), w2[:, :N - 8].contiguous().cuda(), None, gate=gate)
+
+
+def test_sliced_keyformer_problem_sees_the_whole_problems_noise():
+    """A rank that runs only some (batch item, head) units of a KeyFormer problem with generated noise passes the whole
+    problem's head count and its first unit's flat index: its slice of the per-key scores must equal the unsliced
+    run's bit for bit (same noise, same kernels)."""
+    from gpu_util import run_block
+    B, M, P, Hq, Hkv, D, dt = 3, 200, 56, 8, 4, 64, BF
+    q, kc, vc = _attn_inputs(B, M, P, Hq, Hkv, D, dt, seed=41)
+    t = dict(Q=q, K_cache=kc, V_cache=vc, noise=None)
+    kw = dict(M=M, P=P, D=D, causal=True, scale=D ** -0.5, tau=1.0, noise_mode=L.TRN_NOISE_GUMBEL, seed=5, project=False)
+    full = run_block("keyformer", t, B=B, Hq=Hq, Hkv=Hkv, **kw)
+    grp = Hq // Hkv
+    for b0, nb, kv0, kv1 in ((1, 2, 0, 4), (2, 1, 1, 3), (0, 1, 3, 4)):
+        h0, h1 = kv0 * grp, kv1 * grp
+        ts = dict(Q=q[b0:b0 + nb, :, h0:h1].contiguous(), K_cache=kc[b0:b0 + nb, kv0:kv1].contiguous(),
+                  V_cache=vc[b0:b0 + nb, kv0:kv1].contiguous(), noise=None)
+        part = run_block("keyformer", ts, B=nb, Hq=h1 - h0, Hkv=kv1 - kv0, noise_heads=Hq, noise_bh0=b0 * Hq + h0, **kw)
+        assert torch.equal(part["sum_p"], full["sum_p"][b0:b0 + nb, h0:h1])
+        assert torch.equal(part["out"], full["out"][b0:b0 + nb, :, h0:h1])

@@ -80,6 +80,7 @@ class TrnAttnArgs(C.Structure):
         ("noise_stride_i", C.c_int64), ("seed", C.c_uint64), ("single_p", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("lse_pert", C.c_void_p), ("scores", C.c_void_p), ("score_pitch", C.c_int64),
+        ("noise_heads", C.c_int), ("noise_bh0", C.c_int),
     ]
 
 
@@ -92,7 +93,7 @@ class TrnColStatsArgs(C.Structure):
         ("noise_mode", C.c_int), ("tau", C.c_float),
         ("noise", C.c_void_p), ("noise_stride_b", C.c_int64), ("noise_stride_h", C.c_int64),
         ("noise_stride_i", C.c_int64), ("seed", C.c_uint64),
-        ("scores", C.c_void_p), ("score_pitch", C.c_int64),
+        ("scores", C.c_void_p), ("score_pitch", C.c_int64), ("noise_heads", C.c_int), ("noise_bh0", C.c_int),
     ]
 
 
@@ -118,6 +119,7 @@ class TrnBlockArgs(C.Structure):
         ("seed", C.c_uint64),
         ("sum_p", C.c_void_p), ("sum_p2", C.c_void_p), ("stats_fp32", C.c_int), ("single_p", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("keep_scores", C.c_int),
+        ("noise_heads", C.c_int), ("noise_bh0", C.c_int),
     ]
 
 

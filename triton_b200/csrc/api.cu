@@ -208,8 +208,6 @@ int host_chunk_count(const TrnBlockHostArgs& a) {
   if ((d.sum_p != nullptr || d.sum_p2 != nullptr) &&
       a.stats_bytes != 0 && a.stats_bytes != static_cast<size_t>(d.B) * d.Hq * (d.P + d.M) * (d.stats_fp32 ? 4 : 2))
     return 1;
-  // generated KeyFormer noise is keyed by the batch index inside a launch: keep such a block in one pass
-  if (d.variant == TRN_KEYFORMER && d.noise_mode == TRN_NOISE_GUMBEL) return 1;
   return d.B < kHostMaxChunks ? d.B : kHostMaxChunks;
 }
 
@@ -467,6 +465,8 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
     at.noise_stride_h = a->noise_stride_h;
     at.noise_stride_i = a->noise_stride_i;
     at.seed = a->seed;
+    at.noise_heads = a->noise_heads;
+    at.noise_bh0 = a->noise_bh0;
     at.lse_pert = lse_pert;
   }
   rc = launch_attention(at, st, *ds);
@@ -497,6 +497,8 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
     cs.noise_stride_h = a->noise_stride_h;
     cs.noise_stride_i = a->noise_stride_i;
     cs.seed = a->seed;
+    cs.noise_heads = a->noise_heads;
+    cs.noise_bh0 = a->noise_bh0;
     if (keep_scores) {
       cs.scores = at.scores;
       cs.score_pitch = at.score_pitch;
@@ -561,6 +563,9 @@ int trinity_attn_block_host(const TrnBlockHostArgs* a, void* cuda_stream) {
       const size_t stats_dev_item = static_cast<size_t>(d.Hq) * (d.P + d.M) * stat_esz;
       c.sum_p = adv(d.sum_p, stats_dev_item);
       c.sum_p2 = adv(d.sum_p2, stats_dev_item);
+      // generated KeyFormer noise is indexed by the batch item of the uncut problem
+      c.noise_heads = d.noise_heads > 0 ? d.noise_heads : d.Hq;
+      c.noise_bh0 = d.noise_bh0 + b0 * c.noise_heads;
       TRN_CUDA_TRY(cudaStreamWaitEvent(st, hp->ev[1 + 2 * n], 0));
       int rc = trinity_attn_block(&c, cuda_stream);
       if (rc != TRN_OK) {

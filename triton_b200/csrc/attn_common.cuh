@@ -147,7 +147,8 @@ struct NoiseSrc {
   const void* ptr;           // tensor mode
   long long sb, sh, si;      // element strides of (b, h, i); j contiguous
   unsigned long long seed;   // gumbel mode
-  long long M, L, Hq;        // field extents
+  long long M, L, Hq;        // field extents (Hq: query heads of the WHOLE field, of which a launch may hold a slice)
+  long long bh0;             // b * Hq + h of the launch's first (batch item, head) inside the whole field
 };
 
 // noise of element (b, h, i, j); `rowhash` is noise_rowhash(noise_headkey(seed, b*Hq+h), i)

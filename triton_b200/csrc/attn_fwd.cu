@@ -382,7 +382,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = true;
     uint32_t r[32];
     const uint32_t rowhash =
-        (kPert || kPertT1) ? noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)),
+        (kPert || kPertT1) ? noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.noise.Hq + h + p.noise.bh0)),
                               static_cast<uint32_t>(q_abs))
               : 0u;
     // state of the perturbed log-sum-exp, and where this row's scores go when they are kept
@@ -1075,7 +1075,9 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   p.noise.ptr = a.noise;
   p.noise.sb = a.noise_stride_b; p.noise.sh = a.noise_stride_h; p.noise.si = a.noise_stride_i;
   p.noise.seed = a.seed;
-  p.noise.M = a.M; p.noise.L = L; p.noise.Hq = a.Hq;
+  p.noise.M = a.M; p.noise.L = L;
+  p.noise.Hq = a.noise_heads > 0 ? a.noise_heads : a.Hq;
+  p.noise.bh0 = a.noise_bh0;
   p.noise_vec_ok = (a.noise != nullptr && aligned16(a.noise) && (a.noise_stride_b & 7) == 0 &&
                     (a.noise_stride_h & 7) == 0 && (a.noise_stride_i & 7) == 0)
                        ? 1

@@ -226,7 +226,7 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     float* my_lse = lse_s + ((warp - 2) * 2) * 64;
     uint32_t* my_hash = hash_s + ((warp - 2) * 2) * 64;
     float2* part = reinterpret_cast<float2*>(smem_gen + SM::kPartOff) + t * 128 + row;
-    const uint32_t headkey = PERT ? noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.Hq + h)) : 0u;
+    const uint32_t headkey = PERT ? noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.noise.Hq + h + p.noise.bh0)) : 0u;
     float2 acc1 = make_float2(0.f, 0.f), acc2 = make_float2(0.f, 0.f);
     bool ok = true;
     uint32_t r[32];
@@ -470,7 +470,9 @@ int launch_inst(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds
   p.noise.ptr = a.noise;
   p.noise.sb = a.noise_stride_b; p.noise.sh = a.noise_stride_h; p.noise.si = a.noise_stride_i;
   p.noise.seed = a.seed;
-  p.noise.M = a.M; p.noise.L = L; p.noise.Hq = a.Hq;
+  p.noise.M = a.M; p.noise.L = L;
+  p.noise.Hq = a.noise_heads > 0 ? a.noise_heads : a.Hq;
+  p.noise.bh0 = a.noise_bh0;
   p.status = ds.status;
   auto kern = attn_colstats_kernel<T, D, PERT>;
   rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);

@@ -249,7 +249,8 @@ class BlockPlan:
                  gamma_k: Optional[torch.Tensor] = None,
                  noise_mode: int = L.TRN_NOISE_NONE, tau: float = 1.0, noise: Optional[torch.Tensor] = None,
                  seed: int = 0, sum_p: Optional[torch.Tensor] = None, sum_p2: Optional[torch.Tensor] = None,
-                 single_p: bool = False, x_norm: Optional[torch.Tensor] = None, keep_scores: int = 0):
+                 single_p: bool = False, x_norm: Optional[torch.Tensor] = None, keep_scores: int = 0,
+                 noise_heads: int = 0, noise_bh0: int = 0):
         _need_cuda(q, k_cache, v_cache, o, x, wq, wk, wv, pre_gamma, gamma_q, gamma_k, noise, sum_p, sum_p2, x_norm)
         self.variant = variant
         skip = x is None
@@ -290,6 +291,8 @@ class BlockPlan:
         a.single_p = int(single_p)
         # KeyFormer / RoCo statistics: 0 = by size, 1 = from scores kept in the workspace, -1 = second q k^T pass
         a.keep_scores = int(keep_scores)
+        # generated noise of a slice of a larger problem: the whole problem's head count and the slice's first (b, h)
+        a.noise_heads, a.noise_bh0 = int(noise_heads), int(noise_bh0)
         lib = L.load()
         nbytes = lib.trinity_attn_block_workspace(C.byref(a))
         self._ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
