@@ -2,6 +2,7 @@
 // state, TMA descriptor construction and the composition of the kernels into the whole attention
 // block the reference's generated forward() computes (TritonGen.py:590-708).
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -43,6 +44,11 @@ int load_encode_fn() {
 }
 
 }  // namespace
+
+bool pdl_enabled() {
+  const char* v = getenv("TRINITY_NO_PDL");        // read per launch: a process may switch it between calls
+  return !(v != nullptr && v[0] != '\0' && v[0] != '0');
+}
 
 int record_cuda_error(cudaError_t e, const char* where) {
   snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));

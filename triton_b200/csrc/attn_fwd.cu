@@ -166,6 +166,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  // everything above overlapped the previous kernel's tail (the projection that writes q / k / v); from here on its
+  // results are read.  The next kernel (merge, statistics) may start its own prologue.
+  griddep_wait();
+  griddep_launch();
 
   // ---- which two tiles: heavy (late) query blocks first so the causal tail is short
   const int split = static_cast<int>(blockIdx.x) / p.ctas_per_split;
@@ -967,6 +971,8 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
                     long long o_sb, long long o_ss, long long o_sh, float* __restrict__ lse_out,
                     const float* __restrict__ part_lse2, float* __restrict__ lse2_out, int n_splits, int B,
                     int Hq, int M, const int* __restrict__ status) {
+  griddep_wait();
+  griddep_launch();
   if (*reinterpret_cast<const volatile int*>(status) != 0) return;
   constexpr int VPL = D / 32;
   const long long rows = static_cast<long long>(B) * Hq * M;
@@ -1108,15 +1114,15 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
     p.part_lse2 = reinterpret_cast<float*>(ws + l_b);
     p.part_o = (MODE != 1) ? reinterpret_cast<float*>(ws + 2 * l_b) : nullptr;
   }
-  kern<<<static_cast<int>(ctas * n_splits), kAttnThreads, SM::kTotal, st>>>(tm_q, tm_k, tm_v, p);
-  TRN_CUDA_TRY(cudaGetLastError());
+  TRN_CUDA_TRY(launch_pdl(kern, dim3(static_cast<unsigned>(ctas * n_splits)), dim3(kAttnThreads), SM::kTotal, st, tm_q, tm_k,
+                          tm_v, p));
   if (n_parts > 1) {
     const int warps_per_cta = 8;
     const long long cgrid = (rows + warps_per_cta - 1) / warps_per_cta;
-    attn_combine_kernel<T, D><<<static_cast<int>(cgrid), warps_per_cta * 32, 0, st>>>(
-        p.part_o, p.part_lse, static_cast<T*>(a.o.ptr), a.o.stride_b, a.o.stride_s, a.o.stride_h, a.lse,
-        (MODE == 2 || MODE == 4) ? p.part_lse2 : nullptr, a.lse_pert, n_parts, a.B, a.Hq, a.M, ds.status);
-    TRN_CUDA_TRY(cudaGetLastError());
+    TRN_CUDA_TRY(launch_pdl(attn_combine_kernel<T, D>, dim3(static_cast<unsigned>(cgrid)), dim3(warps_per_cta * 32), 0, st,
+                            p.part_o, p.part_lse, static_cast<T*>(a.o.ptr), a.o.stride_b, a.o.stride_s, a.o.stride_h, a.lse,
+                            (MODE == 2 || MODE == 4) ? p.part_lse2 : nullptr, a.lse_pert, n_parts, a.B, a.Hq, a.M,
+                            ds.status));
   }
   return TRN_OK;
 }

@@ -118,6 +118,8 @@ attn_colstats_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  griddep_wait();          // the attention pass's log-sum-exp values are read from here on
+  griddep_launch();
 
   // ---- which two tiles: early key blocks (seen by the most queries under a causal mask) first
   const int row_blk = static_cast<int>(blockIdx.x) / p.units;
@@ -389,6 +391,8 @@ __global__ void __launch_bounds__(256)
 colstats_from_scores_kernel(const float* __restrict__ scores, long long pitch, const float* __restrict__ lse,
                             void* __restrict__ sum_p, void* __restrict__ sum_p2, int M, int L, int first_query_off,
                             int stats_fp32, const int* __restrict__ status) {
+  griddep_wait();
+  griddep_launch();
   if (*reinterpret_cast<const volatile int*>(status) != 0) return;
   const int key = blockIdx.x * blockDim.x + threadIdx.x;
   const long long bh = blockIdx.y;
@@ -430,9 +434,9 @@ int launch_from_scores(const TrnColStatsArgs& a, cudaStream_t st, const DeviceSt
   if (bh > 65535) return TRN_E_SHAPE;
   dim3 grid(static_cast<unsigned>((L + 255) / 256), static_cast<unsigned>(bh));
   // non-causal: every query sees every key (offset = L makes key - offset negative for all keys)
-  colstats_from_scores_kernel<T><<<grid, 256, 0, st>>>(a.scores, a.score_pitch, a.lse, a.sum_p, a.sum_p2, a.M, L,
-                                                       a.causal ? a.P : L, a.stats_fp32, ds.status);
-  TRN_CUDA_TRY(cudaGetLastError());
+  TRN_CUDA_TRY(launch_pdl(colstats_from_scores_kernel<T>, grid, dim3(256), 0, st, a.scores,
+                          static_cast<long long>(a.score_pitch), a.lse, a.sum_p, a.sum_p2, a.M, L, a.causal ? a.P : L,
+                          a.stats_fp32, static_cast<const int*>(ds.status)));
   return TRN_OK;
 }
 
@@ -479,7 +483,7 @@ int launch_inst(const TrnColStatsArgs& a, cudaStream_t st, const DeviceState& ds
   if (rc != TRN_OK) return rc;
   const long long grid = rows_of_ctas * p.units;
   if (grid > 0x7fffffffLL) return TRN_E_SHAPE;
-  kern<<<static_cast<int>(grid), kCsThreads, SM::kTotal, st>>>(tm_q, tm_k, p);
+  TRN_CUDA_TRY(launch_pdl(kern, dim3(static_cast<unsigned>(grid)), dim3(kCsThreads), SM::kTotal, st, tm_q, tm_k, p));
   TRN_CUDA_TRY(cudaGetLastError());
   return TRN_OK;
 }

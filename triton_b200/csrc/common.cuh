@@ -97,6 +97,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const C
 }
 
 // ------------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream is still draining.  griddep_wait() returns once every predecessor grid has
+// completed and its writes are visible (at once when the launch carried no such dependency); everything a kernel
+// does before it — barrier set-up, tensor-memory allocation, descriptor prefetch — overlaps the predecessor's tail.
+// griddep_launch() tells the scheduler that the NEXT kernel in the stream may begin its own prologue.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------
 // TMA tile loads (no multicast anywhere in this library: every CTA fetches its own tiles)
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {

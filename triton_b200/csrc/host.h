@@ -42,6 +42,25 @@ int make_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t
 // opts a kernel in to `bytes` of dynamic shared memory, once per (kernel, device)
 int ensure_dyn_smem(const void* kernel, int bytes, int device);
 
+// Launch with the programmatic-stream-serialization attribute (see griddep_wait in common.cuh): the kernel may begin
+// its prologue before the previous kernel of the stream has finished; capturable in CUDA graphs.  TRINITY_NO_PDL=1
+// in the environment makes these plain launches.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // launchers implemented per kernel family

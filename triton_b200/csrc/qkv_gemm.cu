@@ -150,6 +150,10 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  // the set-up above overlapped the previous kernel's tail (PreNorm's row statistics / X_norm); the next kernel
+  // (attention) may begin its own set-up
+  griddep_wait();
+  griddep_launch();
 
   const int k_steps = (p.K + BK - 1) / BK;
   const int k_steps2 = KCAT ? (p.K2 + BK - 1) / BK : 0;
@@ -462,8 +466,7 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
     if (rc != TRN_OK) return rc;
   }
   const int grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
-  kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(tm_x, tm_w[0], tm_w[1], tm_w[2], p);
-  TRN_CUDA_TRY(cudaGetLastError());
+  TRN_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, tm_x, tm_w[0], tm_w[1], tm_w[2], p));
   return TRN_OK;
 }
 

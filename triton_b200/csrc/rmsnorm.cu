@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(kRowCtaThreads)
 rmsnorm_cta_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restrict__ gamma,
                    float* __restrict__ rstd_out, long long rows, int cols, long long x_stride,
                    long long y_stride, float eps) {
+  griddep_launch();        // the projection that follows may set itself up while the rows stream
   __shared__ float partial[2][kRowCtaThreads / 32];
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
