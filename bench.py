@@ -1,6 +1,6 @@
 """Benchmark of the fused attention block on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|flashinfer] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|flashinfer|cublas] [--workload NAME]
                     [--replicas]
 
 One "step" is one call of the whole block (RMSNorm statistics -> QKV projection -> attention
@@ -20,7 +20,8 @@ instead ("weak").
 
 `--impl reference` times the reference's CPU path for the same block (the fp32 PyTorch restatement of ref_rms.py in
 oracle/, all host threads) on the FULL configuration.  `--impl flashinfer` times the attention core of the workload
-with FlashInfer's kernels beside this library's on the same q / k / v, same GPU, same run.
+with FlashInfer's kernels beside this library's on the same q / k / v, same GPU, same run.  `--impl cublas` runs
+cuBLAS (torch.matmul) beside the projection GEMM for about 2.5 s each with the SM clock sampled, to compare per clock.
 """
 from __future__ import annotations
 
@@ -697,6 +698,77 @@ def run_flashinfer(args, w):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------------------------
+# cuBLAS beside this library's projection GEMM: sustained TFLOP/s and the same per sampled SM clock
+# ------------------------------------------------------------------------------------------------
+def run_cublas(args, w):
+    """torch.matmul (cuBLAS) at 8192^3 and at the workload's projection shape, this library's projection and its
+    attention core, each back to back for about 2.5 s in ONE process with the SM clock sampled through NVML every
+    ~0.5 ms: TFLOP/s / median MHz -> multiply-accumulates per clock per SM."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+    from triton_b200 import _lib as L
+    from triton_b200 import ops
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    B, S, N, Hq, Hkv, D = (w[k] for k in ("B", "S", "N", "Hq", "Hkv", "D"))
+    dt = torch.bfloat16
+    out = {}
+
+    def run(name, fn, flops, seconds=2.5):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        n = max(10, int(seconds * 1e3 / (e0.elapsed_time(e1) / 10)))
+        smp = ClockSampler(dev.index, period_s=0.0005)
+        smp.start()
+        time.sleep(0.05)
+        m0 = smp.mark()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        m1 = smp.mark()
+        c = smp.stop()
+        ms, mhz = e0.elapsed_time(e1) / n, smp.median(m0, m1)
+        tf = flops / (ms * 1e-3) / 1e12
+        out[name] = {"ms": ms, "calls": n, "tflops": tf, "sm_mhz_median": mhz, "clock_samples": m1 - m0,
+                     "mac_per_clk_per_sm": tf * 1e12 / 2 / sms / (mhz * 1e6) if mhz else None, "reasons": c["reasons"]}
+
+    a = torch.randn(8192, 8192, device=dev, dtype=dt)
+    b = torch.randn(8192, 8192, device=dev, dtype=dt)
+    c = torch.empty(8192, 8192, device=dev, dtype=dt)
+    run("cublas_8192", lambda: torch.matmul(a, b, out=c), 2 * 8192 ** 3)
+    x = torch.randn(B * S, N, device=dev).to(dt)
+    wq, wk, wv = ((torch.randn(N, h * D, device=dev) / N ** 0.5).to(dt) for h in (Hq, Hkv, Hkv))
+    q = torch.empty(B, S, Hq, D, device=dev, dtype=dt)
+    kc = torch.empty(B, Hkv, S, D, device=dev, dtype=dt)
+    vc = torch.empty(B, Hkv, S, D, device=dev, dtype=dt)
+    qv, kv, vv = ops.as_bshd(q, "bshd"), ops.as_bshd(kc, "bhsd"), ops.as_bshd(vc, "bhsd")
+    pf = 2 * B * S * N * (Hq + 2 * Hkv) * D
+    run("ours_qkv_gemm", lambda: ops.qkv_project(x, wq, wk, wv, q=qv, k_cache=kv, v_cache=vv, B=B, M=S, P=0, Hq=Hq, Hkv=Hkv, D=D), pf)
+    wcat = torch.cat([wq, wk, wv], dim=1).contiguous()
+    oc = torch.empty(B * S, wcat.shape[1], device=dev, dtype=dt)
+    run("cublas_projection_shape", lambda: torch.matmul(x, wcat, out=oc), pf)
+    o = torch.empty_like(q)
+    run("ours_attention", lambda: ops.attention(qv, kv, vv, ops.as_bshd(o, "bshd"), P=0, causal=True, scale=D ** -0.5),
+        4 * B * Hq * D * (S * (S + 1) // 2))
+    if L.kernel_status() != 0:
+        raise RuntimeError("kernel status")
+    print(json.dumps({"impl": "cublas", "metric": "sustained TFLOP/s and MAC per sampled SM clock per SM", "n_gpus": 1,
+                      "sms": sms, "config": {"workload": args.workload, "B": B, "S": S, "N": N, "Hq": Hq, "Hkv": Hkv, "D": D},
+                      "results": out}))
+
+
 def run_rmsnorm(args, w):
     """Standalone RMSNorm: algorithmic bytes = 2 * rows * cols * 2 (read x, write y) + gamma."""
     import torch
@@ -836,7 +908,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", choices=("ours", "reference", "flashinfer"), default="ours")
+    ap.add_argument("--impl", choices=("ours", "reference", "flashinfer", "cublas"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="prenorm_llama")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sustained", action="store_true", help="skip the second (>= 1 s) timed region")
@@ -845,7 +917,11 @@ def main():
     ap.add_argument("--fi-backends", default="fa2,cutlass", help="--impl flashinfer: FlashInfer kernels to time")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "flashinfer":
+    if args.impl == "cublas":
+        if w["variant"] in ("rmsnorm", "native") or not w["project"]:
+            raise SystemExit("--impl cublas needs a workload with a projection")
+        run_cublas(args, w)
+    elif args.impl == "flashinfer":
         if w["variant"] == "rmsnorm":
             raise SystemExit("--impl flashinfer times an attention core")
         run_flashinfer(args, w)

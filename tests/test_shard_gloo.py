@@ -76,3 +76,29 @@ def test_two_rank_shard_and_gather():
         assert p.exitcode == 0
     assert [g[1] for g in got] == [6, 6]        # 12 units split evenly
     assert all(g[2] for g in got)
+
+
+def test_rank_launches_cover_the_problem_once_for_gqa_and_mqa():
+    """What the sharded benchmark binds per rank: batch items x query heads x kv heads, merged over consecutive batch
+    items.  GQA / MHA units are (batch, kv group); with ONE shared kv head (MQA) they are (batch, query head), so that
+    more than B ranks have work and the kv head is replicated."""
+    for B, Hq, Hkv, W in ((8, 32, 8, 8), (8, 32, 8, 2), (8, 32, 8, 3), (4, 71, 1, 8), (2, 71, 1, 8), (1, 32, 8, 8), (4, 32, 8, 8)):
+        seen = set()
+        per_rank = []
+        for r in range(W):
+            ls = shard.rank_launches(B, Hq, Hkv, r, W)
+            per_rank.append(sum(l.nb * (l.h1 - l.h0) for l in ls))
+            for l in ls:
+                grp = Hq // Hkv
+                assert 0 <= l.kv0 < l.kv1 <= Hkv and (l.kv0, l.kv1) == (l.h0 // grp, (l.h1 - 1) // grp + 1)
+                for b in range(l.b0, l.b0 + l.nb):
+                    for h in range(l.h0, l.h1):
+                        assert (b, h) not in seen
+                        seen.add((b, h))
+        assert len(seen) == B * Hq
+        assert abs(sum(shard.launch_flop_share(shard.rank_launches(B, Hq, Hkv, r, W), B, Hq) for r in range(W)) - 1.0) < 1e-12
+        unit = 1 if Hkv == 1 else Hq // Hkv
+        assert max(per_rank) - min(per_rank) <= unit           # balanced to one unit
+    # whole batch items merge into one launch; MQA splits a batch item's heads across ranks
+    assert [(l.b0, l.nb, l.h0, l.h1) for l in shard.rank_launches(8, 32, 8, 1, 2)] == [(4, 4, 0, 32)]
+    assert [(l.b0, l.nb, l.h0, l.h1, l.kv0, l.kv1) for l in shard.rank_launches(4, 71, 1, 1, 8)] == [(0, 1, 36, 71, 0, 1), (1, 1, 0, 1, 0, 1)]
