@@ -401,7 +401,9 @@ def test_candidate_structure_selects_the_statistics_schedule():
     assert outs["kept"][0].SCHEDULE["scores_in_memory"] == ["C_exp"] and "C_exp" in outs["kept"][0].TENSOR_PARAMS
     assert outs["recompute"][0].SCHEDULE["scores_in_memory"] == [] and "C_exp" not in outs["recompute"][0].TENSOR_PARAMS
     assert outs["kept"][0]._op.keep_scores == 1 and outs["recompute"][0]._op.keep_scores == -1
-    assert torch.equal(outs["kept"][1]["O2"], outs["recompute"][1]["O2"])
+    # the two schedules run different attention kernels at 16 queries (scores kept: tensor-memory kernel; nothing kept:
+    # the warp-level one): the same softmax in another summation order
+    assert_parity(outs["recompute"][1]["O2"].cuda().half(), outs["kept"][1]["O2"], "O2: recompute vs kept scores", rel_tol=2e-2)
     for k in ("C_out1", "C_out2"):
         assert_parity(outs["recompute"][1][k].cuda().half(), outs["kept"][1][k], f"{k}: recompute vs kept scores", rel_tol=2e-2)
     assert L.kernel_status() == 0

@@ -55,6 +55,12 @@ PROJ_CASES = [
     (2, 96, 16, 512, 8, 2, 64, BF, True, False),
     (2, 96, 16, 520, 4, 2, 128, HF, True, True),      # hidden size not a multiple of the 64-wide K step
     (1, 16, 1024, 4544, 71, 71, 64, HF, False, False),
+    # at most 32 rows and a long contraction: the cluster split-K kernel
+    (1, 16, 1024, 4096, 32, 32, 128, HF, False, False),   # the reference's Llama shape
+    (2, 16, 16, 1024, 8, 2, 128, BF, True, True),         # 32 rows over two batches, per-head norm, row scale, GQA
+    (1, 9, 0, 4096, 32, 8, 128, HF, True, False),
+    (1, 16, 8, 2048, 16, 4, 64, BF, True, True),          # head_dim 64: a thread's 64 columns are one head
+    (3, 1, 40, 1536, 12, 12, 64, BF, False, True),        # decode rows of three sequences
 ]
 
 
@@ -171,6 +177,51 @@ def test_attention_split_kv_matches_unsplit_and_oracle(B, M, P, Hq, Hkv, D, dt, 
         assert_parity(o1, o0.float().cpu(), "split vs unsplit")
         r = O.attend(q.float().transpose(1, 2), kc.float(), vc.float(), P=P, causal=causal, scale=scale)
         assert_parity(o1, r["out"].transpose(1, 2), "split attention output")
+
+
+SMALL_CASES = [
+    # B, M, P, Hq, Hkv, D, dtype, causal: at most 16 queries per head (the cluster-merged mma.sync kernel)
+    (1, 16, 1024, 32, 32, 128, HF, False),            # the reference's Llama shape: clusters of 4
+    (1, 16, 1024, 71, 71, 64, HF, False),             # the reference's Falcon shape: clusters of 2
+    (1, 1, 4095, 2, 1, 128, BF, True),                # decode, long prefix: clusters of 8
+    (2, 16, 0, 3, 3, 64, BF, True),                   # no prefix: one chunk, three of the four warps see no key
+    (1, 5, 27, 2, 2, 128, HF, True),                  # exactly one chunk of 32 keys
+    (4, 9, 500, 40, 8, 64, BF, True),                 # more heads than SMs: no cluster
+    (1, 16, 8000, 4, 4, 128, HF, False),              # 250 chunks over 32 warps
+    (1, 13, 70, 6, 2, 128, BF, True),                 # GQA, ragged last chunk
+    (8, 1, 4095, 32, 8, 128, BF, True),               # GQA decode: the 4 query heads of a kv head share one CTA's rows
+    (2, 1, 300, 16, 1, 64, HF, True),                 # MQA decode: 16 heads in the 16 rows
+    (1, 4, 200, 8, 2, 128, BF, True),                 # 4 heads x 4 queries: the causal limit follows the query, not the row
+    (1, 3, 100, 12, 2, 64, HF, True),                 # group of 6, 3 queries: packs of 3 heads (9 rows)
+]
+
+
+@pytest.mark.parametrize("B,M,P,Hq,Hkv,D,dt,causal", SMALL_CASES)
+def test_attention_with_at_most_16_queries(B, M, P, Hq, Hkv, D, dt, causal):
+    scale = D ** -0.5
+    q, kc, vc = _attn_inputs(B, M, P, Hq, Hkv, D, dt, seed=21)
+    o, lse = _run_attention(q, kc, vc, P, causal, scale)
+    o2, lse2 = _run_attention(q, kc, vc, P, causal, scale)
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)          # fixed merge order
+    r = O.attend(q.float().transpose(1, 2), kc.float(), vc.float(), P=P, causal=causal, scale=scale)
+    assert not torch.isnan(o).any()
+    assert_parity(o, r["out"].transpose(1, 2), "small-M attention output")
+    sc = torch.matmul(q.float().transpose(1, 2), kc.float().repeat_interleave(Hq // Hkv, 1).transpose(-1, -2)) * scale
+    if causal:
+        i = torch.arange(M).view(M, 1)
+        j = torch.arange(P + M).view(1, P + M)
+        sc = sc.masked_fill(j > i + P, -math.inf)
+    assert (lse.cpu() - torch.logsumexp(sc, -1) / math.log(2)).abs().max().item() <= 1e-4
+    # token-major caches [B, L, Hkv, D] (the layout cache append writes): same numbers, other strides
+    kt, vt = kc.transpose(1, 2).contiguous().cuda(), vc.transpose(1, 2).contiguous().cuda()
+    o3 = torch.zeros_like(o)
+    ops.attention(ops.as_bshd(q.cuda(), "bshd"), ops.as_bshd(kt, "bshd"), ops.as_bshd(vt, "bshd"), ops.as_bshd(o3, "bshd"),
+                  P=P, causal=causal, scale=scale)
+    torch.cuda.synchronize()
+    assert torch.equal(o3, o)
+    # one 16-bit part of p (single_p): looser, still inside the absolute bound
+    o4, _ = _run_attention(q, kc, vc, P, causal, scale, single_p=True)
+    assert parity_errors(o4, r["out"].transpose(1, 2))[0] <= 2e-2
 
 
 def test_attention_workspace_is_zero_for_launches_that_fill_the_gpu():

@@ -20,7 +20,7 @@ INCLUDE = PKG_DIR.parent / "include"
 BUILD_DIR = PKG_DIR / "build"
 LIB_PATH = PKG_DIR / "libtrinity_b200.so"
 
-SOURCES = ["api.cu", "rmsnorm.cu", "qkv_gemm.cu", "attn_fwd.cu", "colstats.cu", "topk.cu", "static_scratch.cu", "convert.cu", "selftest.cu", "lora_small.cu", "gmlp_small.cu"]
+SOURCES = ["api.cu", "rmsnorm.cu", "qkv_gemm.cu", "attn_fwd.cu", "colstats.cu", "topk.cu", "static_scratch.cu", "convert.cu", "selftest.cu", "lora_small.cu", "gmlp_small.cu", "attn_small.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

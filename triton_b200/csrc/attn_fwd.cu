@@ -1220,9 +1220,10 @@ int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& d
   if (a.scores != nullptr) {
     if (a.score_pitch < a.P + a.M || (a.score_pitch & 31) != 0 || !aligned16(a.scores)) return TRN_E_SHAPE;
   }
+  if (a.dtype != TRN_BF16 && a.dtype != TRN_FP16) return TRN_E_DTYPE;
+  if (attn_small_applies(a)) return launch_attn_small(a, st, ds);
   if (a.dtype == TRN_BF16) return launch_typed<__nv_bfloat16>(a, st, ds);
-  if (a.dtype == TRN_FP16) return launch_typed<__half>(a, st, ds);
-  return TRN_E_DTYPE;
+  return launch_typed<__half>(a, st, ds);
 }
 
 }  // namespace trn

@@ -1,0 +1,342 @@
+// Attention core for at most 16 queries per (batch, head) — decode, chunked prefill, the reference's own M = 16,
+// P = 1024 shapes (ref_rms.py:72-81: o = softmax(scale * q k^T) v over the cached prefix plus the new keys).
+//
+// With 16 query rows a 128-row tensor-memory tile is 7/8 padding and the launch is a latency chain (tensor-memory
+// allocation, descriptors, a second launch to merge split-KV partials).  Here a CTA of four warps owns one (batch, head)
+// and 1 / n_splits of its keys; each warp walks its own quarter of that range in chunks of 32 keys through a private
+// two-stage cp.async ring, with warp-level mma.m16n8k16 for s = q k^T (q fragments stay in registers) and o += p v (p is
+// re-used from the score accumulators as the A operand, as hi + lo 16-bit parts), and an online softmax on the
+// accumulator registers.  The four warps' partial (max, sum, o) meet in shared memory, the CTAs of a head — a thread-
+// block cluster — meet in rank 0's shared memory (st.shared::cluster between two cluster barriers), always in the same
+// order: one launch, no scratch, bitwise reproducible.
+//
+// Algorithmic work per launch: 4 * B * Hq * D * M * (visible keys) flop; bytes: q, o and every visible k / v row once.
+#include <math.h>
+
+#include "attn_common.cuh"
+#include "small_mma.cuh"
+
+namespace trn {
+namespace {
+
+constexpr int kAsThreads = 128;
+constexpr int kAsKeys = 32;          // keys per chunk
+constexpr int kAsStages = 2;
+constexpr int kAsMaxSplits = 8;
+
+template <int D>
+struct AsSmem {
+  static constexpr int kPitch = D * 2 + 16;                    // bytes per staged key row: conflict-free ldmatrix
+  static constexpr int kPanel = kAsKeys * kPitch;              // one [32 x D] panel of k or v
+  static constexpr int kWarpRing = kAsStages * 2 * kPanel;
+  static constexpr int kRingBytes = 4 * kWarpRing;
+  // after the key loop the ring is dead: the four warps' partials [4][16][D + 2] fp32 (o, max, sum), then rank 0's
+  // exchange area for the cluster [8][16][D + 2]
+  static constexpr int kRow = D + 2;
+  static constexpr int kPart = 0;
+  static constexpr int kXchg = kPart + 4 * 16 * kRow * 4;
+  static constexpr int kEpilogue = kXchg + kAsMaxSplits * 16 * kRow * 4;
+  static constexpr int kTotal = kRingBytes > kEpilogue ? kRingBytes : kEpilogue;
+};
+
+struct AsParams {
+  const void* q; const void* k; const void* v; void* o;
+  long long q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh;
+  float* lse;
+  int B, M, P, L, Hq, group;
+  int pack;      // query heads of one kv head that share a CTA's 16 rows (pack * M <= 16): row r = (head r / M, query r % M)
+  int causal;
+  float scale_log2;
+  int n_splits;
+};
+
+// HILO: p enters p v as two 16-bit parts (hi + lo, the library's default accuracy); false: one part (single_p callers)
+template <typename T, int D, bool HILO>
+__global__ void __launch_bounds__(kAsThreads)
+attn_small_kernel(const AsParams p) {
+  using SM = AsSmem<D>;
+  constexpr int KS = D / 16;           // k steps of q k^T
+  constexpr int NB = D / 8;            // 8-column blocks of o
+  extern __shared__ __align__(16) uint8_t as_smem[];
+  const uint32_t smem_base = smem_u32(as_smem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t rank = cluster_ctarank();
+  const int unit = static_cast<int>(blockIdx.x) / p.n_splits, units_per_batch = p.Hq / p.pack;
+  const int b = unit / units_per_batch, h0 = (unit - b * units_per_batch) * p.pack, kvh = h0 / p.group;
+  const int n_rows = p.pack * p.M;
+  griddep_wait();                      // q / k / v come from the projection launched before
+  griddep_launch();
+
+  // ---- q fragments: rows g and g + 8 of the (at most 16) queries, all of head_dim
+  const T* qb = static_cast<const T*>(p.q) + b * p.q_sb;
+  const bool row_lo = g < n_rows, row_hi = g + 8 < n_rows;
+  const int hd_lo = row_lo ? g / p.M : 0, hd_hi = row_hi ? (g + 8) / p.M : 0;          // head within the pack
+  const int i_lo = row_lo ? g - hd_lo * p.M : 0, i_hi = row_hi ? g + 8 - hd_hi * p.M : 0;   // query within the head
+  const T* q_lo = qb + (h0 + hd_lo) * p.q_sh + static_cast<long long>(i_lo) * p.q_ss;
+  const T* q_hi = qb + (h0 + hd_hi) * p.q_sh + static_cast<long long>(i_hi) * p.q_ss;
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const uint32_t* lo = reinterpret_cast<const uint32_t*>(q_lo + ks * 16);
+    const uint32_t* hi = reinterpret_cast<const uint32_t*>(q_hi + ks * 16);
+    qa[ks][0] = row_lo ? __ldg(lo + t) : 0u;
+    qa[ks][1] = row_hi ? __ldg(hi + t) : 0u;
+    qa[ks][2] = row_lo ? __ldg(lo + 4 + t) : 0u;
+    qa[ks][3] = row_hi ? __ldg(hi + 4 + t) : 0u;
+  }
+
+  // ---- this warp's chunks of the key range (chunks of 32 keys dealt out evenly to the 4 * n_splits warps)
+  const int kv_end = p.causal ? min(p.L, p.P + p.M) : p.L;       // keys any of the queries can see
+  const int total_chunks = (kv_end + kAsKeys - 1) / kAsKeys;
+  const int n_warps = 4 * p.n_splits, wi = static_cast<int>(rank) * 4 + warp;
+  const int chunk_lo = total_chunks * wi / n_warps, chunk_hi = total_chunks * (wi + 1) / n_warps;
+  const int n_chunks = chunk_hi - chunk_lo;
+  const T* kb = static_cast<const T*>(p.k) + b * p.k_sb + kvh * p.k_sh;
+  const T* vb = static_cast<const T*>(p.v) + b * p.v_sb + kvh * p.v_sh;
+  const uint32_t ring = smem_base + warp * SM::kWarpRing;
+  auto k_stage = [&](int s) { return ring + s * 2 * SM::kPanel; };
+  auto v_stage = [&](int s) { return k_stage(s) + SM::kPanel; };
+  auto load_stage = [&](int chunk) {
+    const int s = chunk % kAsStages;
+    const int key0 = (chunk_lo + chunk) * kAsKeys;
+    constexpr int kSeg = D / 8;                                  // 16-byte segments per key row
+#pragma unroll
+    for (int i = 0; i < kAsKeys * kSeg / 32; ++i) {
+      const int c = i * 32 + lane, row = c / kSeg, seg = c % kSeg;
+      const int key = min(key0 + row, p.L - 1);                  // rows past the last key repeat it (masked below)
+      cp_async16(k_stage(s) + row * SM::kPitch + seg * 16, kb + static_cast<long long>(key) * p.k_ss + seg * 8);
+      cp_async16(v_stage(s) + row * SM::kPitch + seg * 16, vb + static_cast<long long>(key) * p.v_ss + seg * 8);
+    }
+  };
+
+  float oacc[NB][4];
+#pragma unroll
+  for (int i = 0; i < NB; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oacc[i][j] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;     // rows g and g + 8
+  const int lim_lo = p.causal ? min(p.P + i_lo, p.L - 1) : p.L - 1;     // last visible key of each row
+  const int lim_hi = p.causal ? min(p.P + i_hi, p.L - 1) : p.L - 1;
+
+  if (n_chunks > 0) load_stage(0);
+  cp_async_commit();
+  for (int chunk = 0; chunk < n_chunks; ++chunk) {
+    if (chunk + 1 < n_chunks) load_stage(chunk + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    const int s = chunk % kAsStages;
+    const int key0 = (chunk_lo + chunk) * kAsKeys;
+    // ---- s = q k^T for 32 keys: four 8-key blocks
+    float sacc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sacc[i][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+      for (int n2 = 0; n2 < 2; ++n2) {
+        // matrices: (keys n2*16 .. +7, d ks*16 .. +7), (same keys, d + 8), (keys + 8, d), (keys + 8, d + 8)
+        const int key = n2 * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
+        const int dd = ks * 16 + ((lane >> 3) & 1) * 8;
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"(k_stage(s) + key * SM::kPitch + dd * 2));
+        mma16816<T>(sacc[2 * n2], qa[ks], b0, b1);
+        mma16816<T>(sacc[2 * n2 + 1], qa[ks], b2, b3);
+      }
+    }
+    // ---- online softmax on the accumulators (log2 domain); invisible keys -> -inf
+    float mb_lo = -INFINITY, mb_hi = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = key0 + nb * 8 + 2 * t + e;
+        sacc[nb][e] = (key <= lim_lo) ? sacc[nb][e] * p.scale_log2 : -INFINITY;
+        sacc[nb][2 + e] = (key <= lim_hi) ? sacc[nb][2 + e] * p.scale_log2 : -INFINITY;
+        mb_lo = fmaxf(mb_lo, sacc[nb][e]);
+        mb_hi = fmaxf(mb_hi, sacc[nb][2 + e]);
+      }
+    }
+    mb_lo = fmaxf(mb_lo, __shfl_xor_sync(0xffffffffu, mb_lo, 1)); mb_lo = fmaxf(mb_lo, __shfl_xor_sync(0xffffffffu, mb_lo, 2));
+    mb_hi = fmaxf(mb_hi, __shfl_xor_sync(0xffffffffu, mb_hi, 1)); mb_hi = fmaxf(mb_hi, __shfl_xor_sync(0xffffffffu, mb_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mb_lo), mn_hi = fmaxf(m_hi, mb_hi);
+    const float use_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, use_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
+    const float al_lo = ex2_approx(m_lo - use_lo), al_hi = ex2_approx(m_hi - use_hi);     // 0 while m = -inf
+    m_lo = mn_lo; m_hi = mn_hi;
+    float sum_lo = 0.f, sum_hi = 0.f;
+    uint32_t p_hi[4][2], p_lo[4][2];                 // per 8-key block: rows g / g + 8, as packed pairs (hi and lo parts)
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      const float a0 = ex2_approx(sacc[nb][0] - use_lo), a1 = ex2_approx(sacc[nb][1] - use_lo);
+      const float c0 = ex2_approx(sacc[nb][2] - use_hi), c1 = ex2_approx(sacc[nb][3] - use_hi);
+      sum_lo += a0 + a1;
+      sum_hi += c0 + c1;
+      p_hi[nb][0] = Io<T>::pack2(a0, a1);
+      p_hi[nb][1] = Io<T>::pack2(c0, c1);
+      if constexpr (HILO) {
+        const float2 ra = Io<T>::unpack2(p_hi[nb][0]), rc = Io<T>::unpack2(p_hi[nb][1]);
+        p_lo[nb][0] = Io<T>::pack2(a0 - ra.x, a1 - ra.y);
+        p_lo[nb][1] = Io<T>::pack2(c0 - rc.x, c1 - rc.y);
+      }
+    }
+    l_lo = l_lo * al_lo + sum_lo;       // this thread's share of the row sums (its 8 of the chunk's 32 keys)
+    l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+      oacc[i][0] *= al_lo; oacc[i][1] *= al_lo;
+      oacc[i][2] *= al_hi; oacc[i][3] *= al_hi;
+    }
+    // ---- o += p v: two k steps of 16 keys; p's accumulator layout is the A fragment's
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      const uint32_t ah[4] = {p_hi[2 * kk][0], p_hi[2 * kk][1], p_hi[2 * kk + 1][0], p_hi[2 * kk + 1][1]};
+      const uint32_t al[4] = {p_lo[2 * kk][0], p_lo[2 * kk][1], p_lo[2 * kk + 1][0], p_lo[2 * kk + 1][1]};
+#pragma unroll
+      for (int n2 = 0; n2 < NB / 2; ++n2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(v_stage(s) + (kk * 16 + (lane & 15)) * SM::kPitch + (n2 * 16 + (lane >> 4) * 8) * 2, b0, b1, b2, b3);
+        mma16816<T>(oacc[2 * n2], ah, b0, b1);
+        mma16816<T>(oacc[2 * n2 + 1], ah, b2, b3);
+        if constexpr (HILO) {
+          mma16816<T>(oacc[2 * n2], al, b0, b1);
+          mma16816<T>(oacc[2 * n2 + 1], al, b2, b3);
+        }
+      }
+    }
+    __syncwarp();                      // every lane is done with stage s before it is refilled
+  }
+  cp_async_wait<0>();
+  // row sums: the four lanes of a group hold different keys of the same rows
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  __syncthreads();                     // every warp is done with its ring: the partials take its place
+
+  // ---- the four warps' partials -> shared memory [warp][row][D | max | sum]
+  float* part = reinterpret_cast<float*>(as_smem + SM::kPart);
+#pragma unroll
+  for (int n = 0; n < NB; ++n) {
+    *reinterpret_cast<float2*>(part + (warp * 16 + g) * SM::kRow + n * 8 + 2 * t) = make_float2(oacc[n][0], oacc[n][1]);
+    *reinterpret_cast<float2*>(part + (warp * 16 + g + 8) * SM::kRow + n * 8 + 2 * t) = make_float2(oacc[n][2], oacc[n][3]);
+  }
+  if (t == 0) {
+    *reinterpret_cast<float2*>(part + (warp * 16 + g) * SM::kRow + D) = make_float2(m_lo, l_lo);
+    *reinterpret_cast<float2*>(part + (warp * 16 + g + 8) * SM::kRow + D) = make_float2(m_hi, l_hi);
+  }
+  __syncthreads();
+  // thread = (row, D / 8 columns): merge `n` partials laid out [n][16][kRow] in fixed order -> (o, max, sum) of the row
+  const int row = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * (D / 8);
+  constexpr int CW = D / 8;
+  float acc[CW], mx, tot;
+  auto merge = [&](const float* src, int n) {
+    mx = -INFINITY;
+    for (int i = 0; i < n; ++i) mx = fmaxf(mx, src[(i * 16 + row) * SM::kRow + D]);
+    tot = 0.f;
+#pragma unroll
+    for (int c = 0; c < CW; ++c) acc[c] = 0.f;
+    for (int i = 0; i < n; ++i) {
+      const float mi = src[(i * 16 + row) * SM::kRow + D];
+      if (mi == -INFINITY) continue;                 // this part saw no visible key of the row
+      const float w = ex2_approx(mi - mx);
+      tot = fmaf(w, src[(i * 16 + row) * SM::kRow + D + 1], tot);
+#pragma unroll
+      for (int c = 0; c < CW; ++c) acc[c] = fmaf(w, src[(i * 16 + row) * SM::kRow + c0 + c], acc[c]);
+    }
+  };
+  merge(part, 4);
+  if (p.n_splits > 1) {
+    cluster_sync_all_relaxed();        // every CTA of the cluster is past its ring: rank 0's exchange area may be written
+    const uint32_t slot = map_to_rank(smem_base + SM::kXchg, 0) + rank * (16 * SM::kRow * 4);
+#pragma unroll
+    for (int c = 0; c < CW; c += 2) st_cluster_f2(slot + (row * SM::kRow + c0 + c) * 4, acc[c], acc[c + 1]);
+    if ((threadIdx.x & 7) == 0) st_cluster_f2(slot + (row * SM::kRow + D) * 4, mx, tot);
+    cluster_sync_all();                // the parts of every rank have landed in rank 0
+    if (rank != 0) return;
+    merge(reinterpret_cast<const float*>(as_smem + SM::kXchg), p.n_splits);
+  }
+  if (row < n_rows) {
+    const int hd = row / p.M, i = row - hd * p.M, h = h0 + hd;
+    const float inv = tot > 0.f ? 1.0f / tot : 0.f;
+    T* dst = static_cast<T*>(p.o) + b * p.o_sb + static_cast<long long>(i) * p.o_ss + h * p.o_sh + c0;
+#pragma unroll
+    for (int c = 0; c < CW; c += 8) {
+      uint4 v;
+      v.x = Io<T>::pack2(acc[c] * inv, acc[c + 1] * inv); v.y = Io<T>::pack2(acc[c + 2] * inv, acc[c + 3] * inv);
+      v.z = Io<T>::pack2(acc[c + 4] * inv, acc[c + 5] * inv); v.w = Io<T>::pack2(acc[c + 6] * inv, acc[c + 7] * inv);
+      *reinterpret_cast<uint4*>(dst + c) = v;
+    }
+    if (p.lse != nullptr && (threadIdx.x & 7) == 0)
+      p.lse[(static_cast<long long>(b) * p.Hq + h) * p.M + i] = mx + log2f(tot);
+  }
+}
+
+template <typename T, int D, bool HILO>
+int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
+  using SM = AsSmem<D>;
+  auto kern = attn_small_kernel<T, D, HILO>;
+  const int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
+  if (rc != TRN_OK) return rc;
+  AsParams p{};
+  p.q = a.q.ptr; p.k = a.k_cache.ptr; p.v = a.v_cache.ptr; p.o = a.o.ptr;
+  p.q_sb = a.q.stride_b; p.q_ss = a.q.stride_s; p.q_sh = a.q.stride_h;
+  p.k_sb = a.k_cache.stride_b; p.k_ss = a.k_cache.stride_s; p.k_sh = a.k_cache.stride_h;
+  p.v_sb = a.v_cache.stride_b; p.v_ss = a.v_cache.stride_s; p.v_sh = a.v_cache.stride_h;
+  p.o_sb = a.o.stride_b; p.o_ss = a.o.stride_s; p.o_sh = a.o.stride_h;
+  p.lse = a.lse;
+  p.B = a.B; p.M = a.M; p.P = a.P; p.L = a.P + a.M; p.Hq = a.Hq; p.group = a.Hq / a.Hkv;
+  p.causal = a.causal;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  // grouped-query heads of one kv head share the CTA's 16 rows while they fit (decode: M = 1 packs 16 heads)
+  p.pack = 1;
+  for (int c = p.group; c >= 1; --c)
+    if (p.group % c == 0 && c * a.M <= 16) { p.pack = c; break; }
+  // CTAs per unit (= cluster size): fill the SMs once, keep every warp at least two chunks of keys
+  const long long heads = static_cast<long long>(a.B) * (a.Hq / p.pack);
+  const int chunks = (p.L + kAsKeys - 1) / kAsKeys;
+  int ns = kAsMaxSplits;
+  while (ns > 1 && (heads * ns > ds.sm_count || chunks < 8 * ns)) ns >>= 1;
+  p.n_splits = ns;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(heads * ns), 1, 1);
+  cfg.blockDim = dim3(kAsThreads, 1, 1);
+  cfg.dynamicSmemBytes = SM::kTotal;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(ns);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  TRN_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+  return TRN_OK;
+}
+
+}  // namespace
+
+// plain attention (no noise, no kept scores) with at most 16 queries per head
+bool attn_small_applies(const TrnAttnArgs& a) {
+  return a.M <= 16 && a.noise_mode == TRN_NOISE_NONE && a.scores == nullptr && (a.D == 64 || a.D == 128) &&
+         static_cast<long long>(a.B) * a.Hq <= 0x3fffffffLL;
+}
+
+int launch_attn_small(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
+  const bool hilo = a.single_p == 0;
+  if (a.dtype == TRN_BF16) {
+    if (a.D == 128) return hilo ? launch_inst<__nv_bfloat16, 128, true>(a, st, ds) : launch_inst<__nv_bfloat16, 128, false>(a, st, ds);
+    return hilo ? launch_inst<__nv_bfloat16, 64, true>(a, st, ds) : launch_inst<__nv_bfloat16, 64, false>(a, st, ds);
+  }
+  if (a.dtype == TRN_FP16) {
+    if (a.D == 128) return hilo ? launch_inst<__half, 128, true>(a, st, ds) : launch_inst<__half, 128, false>(a, st, ds);
+    return hilo ? launch_inst<__half, 64, true>(a, st, ds) : launch_inst<__half, 64, false>(a, st, ds);
+  }
+  return TRN_E_DTYPE;
+}
+
+}  // namespace trn

@@ -75,6 +75,10 @@ int launch_gmlp_small(const TrnGmlpArgs& a, cudaStream_t st, const DeviceState& 
 bool lora_small_applies(const TrnLoraArgs& a);
 int launch_lora_small(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds);
 int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
+// plain attention with at most 16 queries per head: one latency-oriented launch (attn_small.cu); launch_attention
+// validates the arguments and routes here
+bool attn_small_applies(const TrnAttnArgs& a);
+int launch_attn_small(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
 // split-KV policy of the attention kernel: how many CTAs share one tile pair's key range (1: no split),
 // and the scratch a launch of that shape wants for the partial results (0: it would not split)
 constexpr int kAttnMaxSplits = 8;

@@ -19,6 +19,7 @@
 // compulsory bytes: x + wq + wk + wv + q + k + v once each.
 #include "common.cuh"
 #include "host.h"
+#include "small_mma.cuh"
 
 namespace trn {
 namespace {
@@ -376,6 +377,8 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   }
 }
 
+#include "qkv_splitk.cuh"
+
 // Extra operands of the LoRA form: o = x @ wq + d @ b (wk, wv unused).
 struct KcatOperands {
   const void* d;   // [rows, K2]
@@ -385,7 +388,7 @@ struct KcatOperands {
 
 template <typename T, int BN, int FORM>
 int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, const KcatOperands* kc = nullptr,
-                 int gate = 0) {
+                 int gate = 0, int n_split = 1, int rows_pad = 0) {
   constexpr bool KCAT = (FORM == 1);
   constexpr bool GATED = (FORM == 2);
   using Cfg = GemmCfg<BN>;
@@ -455,11 +458,35 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(rows)};
     const uint64_t strides[2] = {1, static_cast<uint64_t>(a.N)};
-    const uint32_t box[2] = {BK, BM};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(n_split > 1 ? kSkARows : BM)};
     int rc = make_tmap_16bit(&tm_x, a.x, 2, dims, strides, box);
     if (rc != TRN_OK) return rc;
   }
 
+  if constexpr (BN == kSkBN && FORM == 0) {
+    if (n_split > 1) {
+      // at most 32 rows: the contraction of every tile split over a cluster of n_split CTAs (qkv_splitk.cuh)
+      auto sk = qkv_splitk_kernel<T>;
+      int rc = ensure_dyn_smem(reinterpret_cast<const void*>(sk), kSkSmemBytes, ds.device);
+      if (rc != TRN_OK) return rc;
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(static_cast<unsigned>(p.n_tiles_total * n_split), 1, 1);
+      cfg.blockDim = dim3(kSkThreads, 1, 1);
+      cfg.dynamicSmemBytes = kSkSmemBytes;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = static_cast<unsigned>(n_split);
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = pdl_enabled() ? 2 : 1;
+      TRN_CUDA_TRY(cudaLaunchKernelEx(&cfg, sk, tm_x, tm_w[0], tm_w[1], tm_w[2], p, n_split, rows_pad));
+      return TRN_OK;
+    }
+  }
   auto kern = qkv_gemm_kernel<T, BN, FORM>;
   {
     int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes, ds.device);
@@ -470,6 +497,42 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
   return TRN_OK;
 }
 
+// Split of the contraction for at most 32 rows (1: the persistent kernel serves the shape): the split that puts the
+// most CTAs on the device while every tile's cluster is resident at once.  What the device can hold is asked once per
+// cluster size (cudaOccupancyMaxActiveClusters: B200's GPCs do not all hold a multiple of every size).
+template <typename T>
+int splitk_plan(const TrnProjArgs& a, const DeviceState& ds, int* rows_pad) {
+  int tiles = 0, max_split = 1;
+  if (!splitk_shape_ok(a, rows_pad, &tiles, &max_split)) return 1;
+  constexpr int kMaxDev = 64;
+  static int resident[kMaxDev][kSkMaxSplit + 1];      // 0: not asked yet; -1: the query failed
+  if (ds.device < 0 || ds.device >= kMaxDev) return 1;
+  auto sk = qkv_splitk_kernel<T>;
+  if (ensure_dyn_smem(reinterpret_cast<const void*>(sk), kSkSmemBytes, ds.device) != TRN_OK) return 1;
+  int best = 1, best_ctas = 0;
+  for (int ns = 2; ns <= max_split; ++ns) {
+    int& r = resident[ds.device][ns];
+    if (r == 0) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(static_cast<unsigned>(ns * 64), 1, 1);
+      cfg.blockDim = dim3(kSkThreads, 1, 1);
+      cfg.dynamicSmemBytes = kSkSmemBytes;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = static_cast<unsigned>(ns);
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      r = (cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(sk), &cfg) == cudaSuccess && n > 0) ? n : -1;
+      if (r < 0) (void)cudaGetLastError();
+    }
+    if (r >= tiles && tiles * ns > best_ctas) { best = ns; best_ctas = tiles * ns; }
+  }
+  return best;
+}
+
 template <typename T>
 int launch_typed(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
   // A single row tile (M <= 128 tokens: decode / chunked prefill, the reference's own M = 16 shapes) streams
@@ -477,8 +540,12 @@ int launch_typed(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
   // tile is used when it fits in one wave.  Measured with the weights coming from HBM (L2 flushed between
   // calls), M = 16, N = 4096: 32.9 us against 41.0 us; with several row tiles the wide tile wins (M = 512:
   // 37.3 us against 49.6 us).
+  // At most 32 rows: the contraction is split as well (qkv_splitk.cuh), which puts the stream on every SM.
   const long long m_tiles = (static_cast<long long>(a.B) * a.M + BM - 1) / BM;
   const long long n128 = (a.Hq * a.D + 127) / 128 + 2LL * ((a.Hkv * a.D + 127) / 128);
+  int rows_pad = 0;
+  const int n_split = splitk_plan<T>(a, ds, &rows_pad);
+  if (n_split > 1) return launch_tiled<T, 256, 0>(a, st, ds, nullptr, 0, n_split, rows_pad);
   if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, 0>(a, st, ds);
   return launch_tiled<T, 256, 0>(a, st, ds);
 }
