@@ -111,6 +111,11 @@ typedef struct {
  *   q -> q_out, k/v -> rows [P, P+M) of the caches (the reference's cache append).
  * x: [B*M, N] row-major.  w*: [N, heads*D] row-major, used as x @ w (not transposed, ref_rms.py:47).
  * row_scale: fp32 [B*M] or NULL (PreNorm's rsqrt(mean x^2 + eps), applied in the epilogue).
+ * With at most 32 rows (B*M) the weights are treated as CONSTANTS of the stream: the kernel starts reading them while
+ * the kernel launched just before it on the same stream may still be running (programmatic dependent launch), and waits
+ * for that kernel only before it touches x, row_scale and the outputs.  A caller that produces wq / wk / wv with the
+ * launch immediately before this one must put any other launch (or a synchronisation) in between, or set
+ * TRINITY_NO_PDL=1.
  * ---------------------------------------------------------------------------------------------- */
 typedef struct {
   const void* x;
@@ -197,7 +202,9 @@ typedef struct {
   void* workspace;       /* optional device scratch, 256-byte aligned (NULL: none).  With it, a launch that
                             would fill less than half of the SMs divides each tile's key range among several
                             CTAs (split-KV) and merges their partial results with a second small kernel; the
-                            result is the same softmax.  Contents need not be initialised.               */
+                            result is the same softmax.  Contents need not be initialised.  Launches with at most
+                            16 queries per head that produce an output split the key range inside thread-block
+                            clusters instead and do not use it.                                              */
   size_t workspace_bytes; /* a smaller area than trinity_attention_workspace() asks for means fewer splits */
   float* lse_pert;       /* with noise_mode != NONE: when given, ONE pass computes the attention output o, lse of
                             the plain scores (if `lse` is given) and, here, lse of the perturbed scores

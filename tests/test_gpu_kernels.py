@@ -349,6 +349,11 @@ def test_topk_edge_cases():
     (1, 16, 1024, 8, 8, 128, HF, False, L.TRN_NOISE_TENSOR),      # the reference's shape (split-KV with a workspace)
     (2, 200, 72, 6, 2, 64, BF, True, L.TRN_NOISE_GUMBEL),
     (1, 300, 0, 4, 4, 128, BF, True, L.TRN_NOISE_TENSOR),
+    # at most 16 queries: the warp-level kernel's fused / score-keeping modes
+    (1, 16, 1024, 71, 71, 64, HF, False, L.TRN_NOISE_TENSOR),     # the reference's Falcon shape
+    (2, 12, 100, 8, 2, 64, BF, True, L.TRN_NOISE_GUMBEL),         # generated noise, causal, grouped heads (one per CTA)
+    (1, 4, 333, 8, 2, 128, BF, True, L.TRN_NOISE_TENSOR),         # four heads packed in the rows; odd noise row length
+    (3, 1, 95, 4, 1, 128, HF, True, L.TRN_NOISE_TENSOR),          # decode
 ))
 def test_fused_attention_and_perturbed_lse_equals_two_passes_and_kept_scores_give_the_same_statistics(
         B, M, P, Hq, Hkv, D, dt, causal, noise_mode):

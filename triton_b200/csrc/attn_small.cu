@@ -10,6 +10,10 @@
 // block cluster — meet in rank 0's shared memory (st.shared::cluster between two cluster barriers), always in the same
 // order: one launch, no scratch, bitwise reproducible.
 //
+// MODE 2 (KeyFormer, ref_rms.py:172-174) carries a second online log-sum-exp, of the perturbed scores
+// (s * scale + g) / tau, beside the attention; MODE 2 / 3 can write every score they see (perturbed / plain, base-2 log
+// domain, -inf where a causal row must not look) for the per-key statistics kernel to sum from memory.
+//
 // Algorithmic work per launch: 4 * B * Hq * D * M * (visible keys) flop; bytes: q, o and every visible k / v row once.
 #include <math.h>
 
@@ -30,9 +34,9 @@ struct AsSmem {
   static constexpr int kPanel = kAsKeys * kPitch;              // one [32 x D] panel of k or v
   static constexpr int kWarpRing = kAsStages * 2 * kPanel;
   static constexpr int kRingBytes = 4 * kWarpRing;
-  // after the key loop the ring is dead: the four warps' partials [4][16][D + 2] fp32 (o, max, sum), then rank 0's
-  // exchange area for the cluster [8][16][D + 2]
-  static constexpr int kRow = D + 2;
+  // after the key loop the ring is dead: the four warps' partials [4][16][kRow] fp32, then rank 0's exchange area for
+  // the cluster [8][16][kRow]
+  static constexpr int kRow = D + 4;                           // o | max, sum | the perturbed scores' max, sum
   static constexpr int kPart = 0;
   static constexpr int kXchg = kPart + 4 * 16 * kRow * 4;
   static constexpr int kEpilogue = kXchg + kAsMaxSplits * 16 * kRow * 4;
@@ -48,12 +52,22 @@ struct AsParams {
   int causal;
   float scale_log2;
   int n_splits;
+  // MODE 2 / 3
+  float scale, pert_log2;      // perturbed score in the log2 domain: (s * scale + g) * pert_log2, pert_log2 = log2(e) / tau
+  NoiseSrc noise;
+  int noise_pair_ok;           // noise tensor: two neighbouring keys of a row can be fetched as one 32-bit load
+  float* lse_pert;             // MODE 2: [B, Hq, M]
+  float* scores;               // optional [B, Hq, M, score_pitch]
+  long long score_pitch;
 };
 
 // HILO: p enters p v as two 16-bit parts (hi + lo, the library's default accuracy); false: one part (single_p callers)
-template <typename T, int D, bool HILO>
+// MODE 0: attention; 2: attention + log-sum-exp of the perturbed scores (+ those scores kept); 3: attention + plain
+// scores kept
+template <typename T, int D, bool HILO, int MODE>
 __global__ void __launch_bounds__(kAsThreads)
 attn_small_kernel(const AsParams p) {
+  constexpr bool kPert = (MODE == 2);
   using SM = AsSmem<D>;
   constexpr int KS = D / 16;           // k steps of q k^T
   constexpr int NB = D / 8;            // 8-column blocks of o
@@ -119,15 +133,58 @@ attn_small_kernel(const AsParams p) {
   const int lim_lo = p.causal ? min(p.P + i_lo, p.L - 1) : p.L - 1;     // last visible key of each row
   const int lim_hi = p.causal ? min(p.P + i_hi, p.L - 1) : p.L - 1;
 
+  // MODE 2 / 3: the rows' noise and score addresses, state of the perturbed log-sum-exp
+  float m2_lo = -INFINITY, m2_hi = -INFINITY, l2_lo = 0.f, l2_hi = 0.f;
+  const int hq_lo = h0 + hd_lo, hq_hi = h0 + hd_hi;
+  uint32_t rh_lo = 0u, rh_hi = 0u;
+  const T* nz_lo = nullptr;
+  const T* nz_hi = nullptr;
+  float* sc_lo = nullptr;
+  float* sc_hi = nullptr;
+  if constexpr (kPert) {
+    rh_lo = noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.noise.Hq + hq_lo + p.noise.bh0)), static_cast<uint32_t>(i_lo));
+    rh_hi = noise_rowhash(noise_headkey(p.noise.seed, static_cast<uint32_t>(b * p.noise.Hq + hq_hi + p.noise.bh0)), static_cast<uint32_t>(i_hi));
+    if (p.noise.mode == TRN_NOISE_TENSOR) {
+      nz_lo = static_cast<const T*>(p.noise.ptr) + b * p.noise.sb + hq_lo * p.noise.sh + i_lo * p.noise.si;
+      nz_hi = static_cast<const T*>(p.noise.ptr) + b * p.noise.sb + hq_hi * p.noise.sh + i_hi * p.noise.si;
+    }
+  }
+  if constexpr (MODE != 0) {
+    if (p.scores != nullptr) {
+      if (row_lo) sc_lo = p.scores + ((static_cast<long long>(b) * p.Hq + hq_lo) * p.M + i_lo) * p.score_pitch;
+      if (row_hi) sc_hi = p.scores + ((static_cast<long long>(b) * p.Hq + hq_hi) * p.M + i_hi) * p.score_pitch;
+    }
+  }
+
   if (n_chunks > 0) load_stage(0);
   cp_async_commit();
   for (int chunk = 0; chunk < n_chunks; ++chunk) {
     if (chunk + 1 < n_chunks) load_stage(chunk + 1);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncwarp();
     const int s = chunk % kAsStages;
     const int key0 = (chunk_lo + chunk) * kAsKeys;
+    // noise of this thread's 16 scores, requested before the wait for the chunk's k / v
+    float gz[4][4];
+    if constexpr (kPert) {
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        const int key = key0 + nb * 8 + 2 * t;
+        if (p.noise.mode == TRN_NOISE_TENSOR && p.noise_pair_ok && key + 1 < p.L) {
+          const float2 a = Io<T>::unpack2(__ldg(reinterpret_cast<const uint32_t*>(nz_lo + key)));
+          const float2 c = Io<T>::unpack2(__ldg(reinterpret_cast<const uint32_t*>(nz_hi + key)));
+          gz[nb][0] = a.x; gz[nb][1] = a.y; gz[nb][2] = c.x; gz[nb][3] = c.y;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int kk = min(key + e, p.L - 1);
+            gz[nb][e] = noise_at<T>(p.noise, rh_lo, b, hq_lo, i_lo, kk);
+            gz[nb][2 + e] = noise_at<T>(p.noise, rh_hi, b, hq_hi, i_hi, kk);
+          }
+        }
+      }
+    }
+    cp_async_wait<1>();
+    __syncwarp();
     // ---- s = q k^T for 32 keys: four 8-key blocks
     float sacc[4][4];
 #pragma unroll
@@ -149,6 +206,37 @@ attn_small_kernel(const AsParams p) {
         mma16816<T>(sacc[2 * n2 + 1], qa[ks], b2, b3);
       }
     }
+    if constexpr (kPert) {
+      // ---- perturbed scores: online log-sum-exp, optional write-out
+      float tl[4][2], th[4][2];
+      float c_lo = -INFINITY, c_hi = -INFINITY;
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = key0 + nb * 8 + 2 * t + e;
+          tl[nb][e] = (key <= lim_lo) ? (sacc[nb][e] * p.scale + gz[nb][e]) * p.pert_log2 : -INFINITY;
+          th[nb][e] = (key <= lim_hi) ? (sacc[nb][2 + e] * p.scale + gz[nb][2 + e]) * p.pert_log2 : -INFINITY;
+          c_lo = fmaxf(c_lo, tl[nb][e]);
+          c_hi = fmaxf(c_hi, th[nb][e]);
+        }
+        if (sc_lo != nullptr) *reinterpret_cast<float2*>(sc_lo + key0 + nb * 8 + 2 * t) = make_float2(tl[nb][0], tl[nb][1]);
+        if (sc_hi != nullptr) *reinterpret_cast<float2*>(sc_hi + key0 + nb * 8 + 2 * t) = make_float2(th[nb][0], th[nb][1]);
+      }
+      c_lo = fmaxf(c_lo, __shfl_xor_sync(0xffffffffu, c_lo, 1)); c_lo = fmaxf(c_lo, __shfl_xor_sync(0xffffffffu, c_lo, 2));
+      c_hi = fmaxf(c_hi, __shfl_xor_sync(0xffffffffu, c_hi, 1)); c_hi = fmaxf(c_hi, __shfl_xor_sync(0xffffffffu, c_hi, 2));
+      const float n_lo = fmaxf(m2_lo, c_lo), n_hi = fmaxf(m2_hi, c_hi);
+      const float u_lo = (n_lo == -INFINITY) ? 0.f : n_lo, u_hi = (n_hi == -INFINITY) ? 0.f : n_hi;
+      float a_lo = 0.f, a_hi = 0.f;
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        a_lo += ex2_approx(tl[nb][0] - u_lo) + ex2_approx(tl[nb][1] - u_lo);
+        a_hi += ex2_approx(th[nb][0] - u_hi) + ex2_approx(th[nb][1] - u_hi);
+      }
+      l2_lo = l2_lo * ex2_approx(m2_lo - u_lo) + a_lo;
+      l2_hi = l2_hi * ex2_approx(m2_hi - u_hi) + a_hi;
+      m2_lo = n_lo; m2_hi = n_hi;
+    }
     // ---- online softmax on the accumulators (log2 domain); invisible keys -> -inf
     float mb_lo = -INFINITY, mb_hi = -INFINITY;
 #pragma unroll
@@ -160,6 +248,10 @@ attn_small_kernel(const AsParams p) {
         sacc[nb][2 + e] = (key <= lim_hi) ? sacc[nb][2 + e] * p.scale_log2 : -INFINITY;
         mb_lo = fmaxf(mb_lo, sacc[nb][e]);
         mb_hi = fmaxf(mb_hi, sacc[nb][2 + e]);
+      }
+      if constexpr (MODE == 3) {
+        if (sc_lo != nullptr) *reinterpret_cast<float2*>(sc_lo + key0 + nb * 8 + 2 * t) = make_float2(sacc[nb][0], sacc[nb][1]);
+        if (sc_hi != nullptr) *reinterpret_cast<float2*>(sc_hi + key0 + nb * 8 + 2 * t) = make_float2(sacc[nb][2], sacc[nb][3]);
       }
     }
     mb_lo = fmaxf(mb_lo, __shfl_xor_sync(0xffffffffu, mb_lo, 1)); mb_lo = fmaxf(mb_lo, __shfl_xor_sync(0xffffffffu, mb_lo, 2));
@@ -214,6 +306,10 @@ attn_small_kernel(const AsParams p) {
   // row sums: the four lanes of a group hold different keys of the same rows
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  if constexpr (kPert) {
+    l2_lo += __shfl_xor_sync(0xffffffffu, l2_lo, 1); l2_lo += __shfl_xor_sync(0xffffffffu, l2_lo, 2);
+    l2_hi += __shfl_xor_sync(0xffffffffu, l2_hi, 1); l2_hi += __shfl_xor_sync(0xffffffffu, l2_hi, 2);
+  }
   __syncthreads();                     // every warp is done with its ring: the partials take its place
 
   // ---- the four warps' partials -> shared memory [warp][row][D | max | sum]
@@ -226,13 +322,26 @@ attn_small_kernel(const AsParams p) {
   if (t == 0) {
     *reinterpret_cast<float2*>(part + (warp * 16 + g) * SM::kRow + D) = make_float2(m_lo, l_lo);
     *reinterpret_cast<float2*>(part + (warp * 16 + g + 8) * SM::kRow + D) = make_float2(m_hi, l_hi);
+    if constexpr (kPert) {
+      *reinterpret_cast<float2*>(part + (warp * 16 + g) * SM::kRow + D + 2) = make_float2(m2_lo, l2_lo);
+      *reinterpret_cast<float2*>(part + (warp * 16 + g + 8) * SM::kRow + D + 2) = make_float2(m2_hi, l2_hi);
+    }
   }
   __syncthreads();
   // thread = (row, D / 8 columns): merge `n` partials laid out [n][16][kRow] in fixed order -> (o, max, sum) of the row
   const int row = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * (D / 8);
   constexpr int CW = D / 8;
-  float acc[CW], mx, tot;
+  float acc[CW], mx, tot, mx2 = -INFINITY, tot2 = 0.f;
   auto merge = [&](const float* src, int n) {
+    if constexpr (kPert) {
+      mx2 = -INFINITY;
+      for (int i = 0; i < n; ++i) mx2 = fmaxf(mx2, src[(i * 16 + row) * SM::kRow + D + 2]);
+      tot2 = 0.f;
+      for (int i = 0; i < n; ++i) {
+        const float mi = src[(i * 16 + row) * SM::kRow + D + 2];
+        if (mi != -INFINITY) tot2 = fmaf(ex2_approx(mi - mx2), src[(i * 16 + row) * SM::kRow + D + 3], tot2);
+      }
+    }
     mx = -INFINITY;
     for (int i = 0; i < n; ++i) mx = fmaxf(mx, src[(i * 16 + row) * SM::kRow + D]);
     tot = 0.f;
@@ -253,7 +362,10 @@ attn_small_kernel(const AsParams p) {
     const uint32_t slot = map_to_rank(smem_base + SM::kXchg, 0) + rank * (16 * SM::kRow * 4);
 #pragma unroll
     for (int c = 0; c < CW; c += 2) st_cluster_f2(slot + (row * SM::kRow + c0 + c) * 4, acc[c], acc[c + 1]);
-    if ((threadIdx.x & 7) == 0) st_cluster_f2(slot + (row * SM::kRow + D) * 4, mx, tot);
+    if ((threadIdx.x & 7) == 0) {
+      st_cluster_f2(slot + (row * SM::kRow + D) * 4, mx, tot);
+      if constexpr (kPert) st_cluster_f2(slot + (row * SM::kRow + D + 2) * 4, mx2, tot2);
+    }
     cluster_sync_all();                // the parts of every rank have landed in rank 0
     if (rank != 0) return;
     merge(reinterpret_cast<const float*>(as_smem + SM::kXchg), p.n_splits);
@@ -271,13 +383,16 @@ attn_small_kernel(const AsParams p) {
     }
     if (p.lse != nullptr && (threadIdx.x & 7) == 0)
       p.lse[(static_cast<long long>(b) * p.Hq + h) * p.M + i] = mx + log2f(tot);
+    if constexpr (kPert) {
+      if ((threadIdx.x & 7) == 0) p.lse_pert[(static_cast<long long>(b) * p.Hq + h) * p.M + i] = mx2 + log2f(tot2);
+    }
   }
 }
 
-template <typename T, int D, bool HILO>
+template <typename T, int D, bool HILO, int MODE>
 int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   using SM = AsSmem<D>;
-  auto kern = attn_small_kernel<T, D, HILO>;
+  auto kern = attn_small_kernel<T, D, HILO, MODE>;
   const int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
   if (rc != TRN_OK) return rc;
   AsParams p{};
@@ -290,6 +405,20 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   p.B = a.B; p.M = a.M; p.P = a.P; p.L = a.P + a.M; p.Hq = a.Hq; p.group = a.Hq / a.Hkv;
   p.causal = a.causal;
   p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.scale = a.scale;
+  p.pert_log2 = 1.4426950408889634f / a.tau;
+  p.noise.mode = a.noise_mode;
+  p.noise.ptr = a.noise;
+  p.noise.sb = a.noise_stride_b; p.noise.sh = a.noise_stride_h; p.noise.si = a.noise_stride_i;
+  p.noise.seed = a.seed;
+  p.noise.M = a.M; p.noise.L = p.L;
+  p.noise.Hq = a.noise_heads > 0 ? a.noise_heads : a.Hq;
+  p.noise.bh0 = a.noise_bh0;
+  p.noise_pair_ok = (a.noise != nullptr && (reinterpret_cast<uintptr_t>(a.noise) & 3u) == 0 && (a.noise_stride_b & 1) == 0 &&
+                     (a.noise_stride_h & 1) == 0 && (a.noise_stride_i & 1) == 0) ? 1 : 0;
+  p.lse_pert = a.lse_pert;
+  p.scores = a.scores;
+  p.score_pitch = a.score_pitch;
   // grouped-query heads of one kv head share the CTA's 16 rows while they fit (decode: M = 1 packs 16 heads)
   p.pack = 1;
   for (int c = p.group; c >= 1; --c)
@@ -318,24 +447,25 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   return TRN_OK;
 }
 
+template <typename T, int D>
+int launch_mode(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
+  if (a.noise_mode != TRN_NOISE_NONE) return launch_inst<T, D, true, 2>(a, st, ds);
+  if (a.scores != nullptr) return launch_inst<T, D, true, 3>(a, st, ds);
+  return a.single_p == 0 ? launch_inst<T, D, true, 0>(a, st, ds) : launch_inst<T, D, false, 0>(a, st, ds);
+}
+
 }  // namespace
 
-// plain attention (no noise, no kept scores) with at most 16 queries per head
+// at most 16 queries per head: plain attention (scores kept or not), or attention fused with the perturbed scores'
+// log-sum-exp; the perturbed-lse-only pass (no output) stays with the tensor-memory kernel
 bool attn_small_applies(const TrnAttnArgs& a) {
-  return a.M <= 16 && a.noise_mode == TRN_NOISE_NONE && a.scores == nullptr && (a.D == 64 || a.D == 128) &&
-         static_cast<long long>(a.B) * a.Hq <= 0x3fffffffLL;
+  if (a.noise_mode != TRN_NOISE_NONE && a.lse_pert == nullptr) return false;
+  return a.M <= 16 && (a.D == 64 || a.D == 128) && static_cast<long long>(a.B) * a.Hq <= 0x3fffffffLL;
 }
 
 int launch_attn_small(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
-  const bool hilo = a.single_p == 0;
-  if (a.dtype == TRN_BF16) {
-    if (a.D == 128) return hilo ? launch_inst<__nv_bfloat16, 128, true>(a, st, ds) : launch_inst<__nv_bfloat16, 128, false>(a, st, ds);
-    return hilo ? launch_inst<__nv_bfloat16, 64, true>(a, st, ds) : launch_inst<__nv_bfloat16, 64, false>(a, st, ds);
-  }
-  if (a.dtype == TRN_FP16) {
-    if (a.D == 128) return hilo ? launch_inst<__half, 128, true>(a, st, ds) : launch_inst<__half, 128, false>(a, st, ds);
-    return hilo ? launch_inst<__half, 64, true>(a, st, ds) : launch_inst<__half, 64, false>(a, st, ds);
-  }
+  if (a.dtype == TRN_BF16) return a.D == 128 ? launch_mode<__nv_bfloat16, 128>(a, st, ds) : launch_mode<__nv_bfloat16, 64>(a, st, ds);
+  if (a.dtype == TRN_FP16) return a.D == 128 ? launch_mode<__half, 128>(a, st, ds) : launch_mode<__half, 64>(a, st, ds);
   return TRN_E_DTYPE;
 }
 
