@@ -61,6 +61,9 @@ PROJ_CASES = [
     (1, 9, 0, 4096, 32, 8, 128, HF, True, False),
     (1, 16, 8, 2048, 16, 4, 64, BF, True, True),          # head_dim 64: a thread's 64 columns are one head
     (3, 1, 40, 1536, 12, 12, 64, BF, False, True),        # decode rows of three sequences
+    # wider than the device holds clusters of 256-column tiles for: 384-column tiles (1.5 / 3 heads of 128, 6 of 64)
+    (1, 16, 8, 512, 64, 64, 128, BF, True, True),
+    (2, 10, 0, 640, 128, 128, 64, HF, True, False),
 ]
 
 

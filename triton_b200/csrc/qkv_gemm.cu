@@ -391,7 +391,6 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
                  int gate = 0, int n_split = 1, int rows_pad = 0) {
   constexpr bool KCAT = (FORM == 1);
   constexpr bool GATED = (FORM == 2);
-  using Cfg = GemmCfg<BN>;
   GemmParams p{};
   p.gate = gate;
   const int rows = a.B * a.M;
@@ -463,16 +462,16 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
     if (rc != TRN_OK) return rc;
   }
 
-  if constexpr (BN == kSkBN && FORM == 0) {
-    if (n_split > 1) {
+  if constexpr ((BN == 256 || BN == 384) && FORM == 0) {
+    if (n_split > 1 || BN == 384) {
       // at most 32 rows: the contraction of every tile split over a cluster of n_split CTAs (qkv_splitk.cuh)
-      auto sk = qkv_splitk_kernel<T>;
-      int rc = ensure_dyn_smem(reinterpret_cast<const void*>(sk), kSkSmemBytes, ds.device);
+      auto sk = qkv_splitk_kernel<T, BN>;
+      int rc = ensure_dyn_smem(reinterpret_cast<const void*>(sk), SkCfg<BN>::kSmemBytes, ds.device);
       if (rc != TRN_OK) return rc;
       cudaLaunchConfig_t cfg{};
       cfg.gridDim = dim3(static_cast<unsigned>(p.n_tiles_total * n_split), 1, 1);
       cfg.blockDim = dim3(kSkThreads, 1, 1);
-      cfg.dynamicSmemBytes = kSkSmemBytes;
+      cfg.dynamicSmemBytes = SkCfg<BN>::kSmemBytes;
       cfg.stream = st;
       cudaLaunchAttribute attr[2];
       attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -487,36 +486,40 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
       return TRN_OK;
     }
   }
-  auto kern = qkv_gemm_kernel<T, BN, FORM>;
-  {
-    int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes, ds.device);
-    if (rc != TRN_OK) return rc;
+  if constexpr (BN != 384) {
+    using Cfg = GemmCfg<BN>;
+    auto kern = qkv_gemm_kernel<T, BN, FORM>;
+    {
+      int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes, ds.device);
+      if (rc != TRN_OK) return rc;
+    }
+    const int grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
+    TRN_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, tm_x, tm_w[0], tm_w[1], tm_w[2], p));
   }
-  const int grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
-  TRN_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, tm_x, tm_w[0], tm_w[1], tm_w[2], p));
   return TRN_OK;
 }
 
-// Split of the contraction for at most 32 rows (1: the persistent kernel serves the shape): the split that puts the
-// most CTAs on the device while every tile's cluster is resident at once.  What the device can hold is asked once per
-// cluster size (cudaOccupancyMaxActiveClusters: B200's GPCs do not all hold a multiple of every size).
-template <typename T>
-int splitk_plan(const TrnProjArgs& a, const DeviceState& ds, int* rows_pad) {
-  int tiles = 0, max_split = 1;
-  if (!splitk_shape_ok(a, rows_pad, &tiles, &max_split)) return 1;
+// Tile width and split of the contraction for at most 32 rows (split 1: the persistent kernel serves the shape): the
+// pair that puts the most CTAs on the device while every tile's cluster is resident at once.  What the device can hold
+// is asked once per tile width and cluster size (cudaOccupancyMaxActiveClusters: B200's GPCs do not all hold a
+// multiple of every size).
+template <typename T, int BN>
+void splitk_plan_bn(const TrnProjArgs& a, const DeviceState& ds, int* best_bn, int* best_split, int* best_ctas, int* rows_pad) {
+  int tiles = 0, max_split = 1, rp = 0;
+  if (!splitk_shape_ok<BN>(a, &rp, &tiles, &max_split)) return;
+  *rows_pad = rp;
   constexpr int kMaxDev = 64;
   static int resident[kMaxDev][kSkMaxSplit + 1];      // 0: not asked yet; -1: the query failed
-  if (ds.device < 0 || ds.device >= kMaxDev) return 1;
-  auto sk = qkv_splitk_kernel<T>;
-  if (ensure_dyn_smem(reinterpret_cast<const void*>(sk), kSkSmemBytes, ds.device) != TRN_OK) return 1;
-  int best = 1, best_ctas = 0;
+  if (ds.device < 0 || ds.device >= kMaxDev) return;
+  auto sk = qkv_splitk_kernel<T, BN>;
+  if (ensure_dyn_smem(reinterpret_cast<const void*>(sk), SkCfg<BN>::kSmemBytes, ds.device) != TRN_OK) return;
   for (int ns = 2; ns <= max_split; ++ns) {
     int& r = resident[ds.device][ns];
     if (r == 0) {
       cudaLaunchConfig_t cfg{};
       cfg.gridDim = dim3(static_cast<unsigned>(ns * 64), 1, 1);
       cfg.blockDim = dim3(kSkThreads, 1, 1);
-      cfg.dynamicSmemBytes = kSkSmemBytes;
+      cfg.dynamicSmemBytes = SkCfg<BN>::kSmemBytes;
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeClusterDimension;
       attr[0].val.clusterDim.x = static_cast<unsigned>(ns);
@@ -528,9 +531,8 @@ int splitk_plan(const TrnProjArgs& a, const DeviceState& ds, int* rows_pad) {
       r = (cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(sk), &cfg) == cudaSuccess && n > 0) ? n : -1;
       if (r < 0) (void)cudaGetLastError();
     }
-    if (r >= tiles && tiles * ns > best_ctas) { best = ns; best_ctas = tiles * ns; }
+    if (r >= tiles && tiles * ns > *best_ctas) { *best_bn = BN; *best_split = ns; *best_ctas = tiles * ns; }
   }
-  return best;
 }
 
 template <typename T>
@@ -543,8 +545,14 @@ int launch_typed(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
   // At most 32 rows: the contraction is split as well (qkv_splitk.cuh), which puts the stream on every SM.
   const long long m_tiles = (static_cast<long long>(a.B) * a.M + BM - 1) / BM;
   const long long n128 = (a.Hq * a.D + 127) / 128 + 2LL * ((a.Hkv * a.D + 127) / 128);
-  int rows_pad = 0;
-  const int n_split = splitk_plan<T>(a, ds, &rows_pad);
+  int rows_pad = 0, bn = 0, n_split = 1, ctas = 0;
+  // 256-column tiles where the device can hold a cluster per tile; 384-column tiles only for projections too wide for
+  // that (measured, weights from HBM: Llama M16 32.5 us with 256 x 2 on 96 CTAs against 37.0 with 384 x 4 on 132 —
+  // more SMs do not help once the stream is DRAM-bound, the larger exchange costs — but N 8192, 3 x 8192 columns:
+  // 86.8 us with 384 x 2 against 105.3 for the persistent kernel, where 96 tiles of 256 find no resident split)
+  splitk_plan_bn<T, 256>(a, ds, &bn, &n_split, &ctas, &rows_pad);
+  if (n_split == 1) splitk_plan_bn<T, 384>(a, ds, &bn, &n_split, &ctas, &rows_pad);
+  if (n_split > 1 && bn == 384) return launch_tiled<T, 384, 0>(a, st, ds, nullptr, 0, n_split, rows_pad);
   if (n_split > 1) return launch_tiled<T, 256, 0>(a, st, ds, nullptr, 0, n_split, rows_pad);
   if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, 0>(a, st, ds);
   return launch_tiled<T, 256, 0>(a, st, ds);

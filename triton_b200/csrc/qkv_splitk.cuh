@@ -7,8 +7,10 @@
 //   * a stage holds only 32 rows of x (4 KiB) beside its 64 x 256 weight block, so six stages fit: 192 KiB of weights
 //     in flight per CTA.  The 128-row MMA reads the 96 rows past the x tile from the weight block that follows it in
 //     the stage; those accumulator rows are never looked at;
-//   * a 128 x 256 tile's contraction is cut into n_split ranges, one CTA each, the CTAs of a tile forming a thread-
-//     block cluster (n_split is the largest for which the device can hold a cluster per tile at once).
+//   * a tile's contraction is cut into n_split ranges, one CTA each, the CTAs of a tile forming a thread-block
+//     cluster.  The device holds only so many clusters of a size at once (B200: 74 of 2, 45 of 3, 33 of 4), so the
+//     split is the largest with a resident cluster per 256-column tile (Llama's 48 tiles: 2); projections with more
+//     than 74 such tiles use 384-column tiles (two MMAs per k step, four stages).
 // Every CTA accumulates its range in tensor memory like the persistent kernel (TMA ring -> tcgen05.mma), then hands
 // its first rows_pad accumulator rows as fp32 to rank 0's shared memory (st.shared::cluster between two cluster
 // barriers; the operand ring is dead by then and is reused).  Rank 0 adds the parts in rank order — bitwise reproducible — and runs the usual epilogue (row
@@ -17,21 +19,27 @@
 // launch): weights are never written by the stream's kernels; x, the row scales and the outputs are touched after it.
 
 constexpr int kSkThreads = 128;
-constexpr int kSkBN = 256;
-constexpr int kSkStages = 6;
 constexpr int kSkARows = 32;                 // rows of x per stage (the TMA box; rows past the last one are zero-filled)
 constexpr int kSkABytes = kSkARows * BK * 2; // 4 KiB
-constexpr int kSkStageBytes = kSkABytes + (kSkBN / 64) * kBBlockBytes;   // 36 KiB
-constexpr int kSkSmemBytes = kSkStages * kSkStageBytes + kBarBytes + 1024;
-constexpr int kSkPitch = kSkBN + 4;          // fp32 words per partial row: 16-byte stores of a warp spread over all banks
 constexpr int kSkMaxSplit = 8;
 
-template <typename T>
+template <int BN>
+struct SkCfg {
+  static constexpr int kStages = (BN == 256) ? 6 : 4;
+  static constexpr int kStageBytes = kSkABytes + (BN / 64) * kBBlockBytes;   // 36 / 52 KiB
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  static constexpr int kSmemBytes = kRingBytes + kBarBytes + 1024;
+  static constexpr int kPitch = BN + 4;      // fp32 words per partial row: 16-byte stores of a warp spread over all banks
+  static constexpr int kTmemCols = (BN == 256) ? 256 : 512;
+};
+
+template <typename T, int BN>
 __global__ void __launch_bounds__(kSkThreads, 1)
 qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w0,
                   const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2,
                   const __grid_constant__ GemmParams p, const int n_split, const int rows_pad) {
-  constexpr int kStageBytes = kSkStageBytes;
+  using Cfg = SkCfg<BN>;
+  constexpr int kSkBN = BN, kSkStages = Cfg::kStages, kStageBytes = Cfg::kStageBytes, kSkPitch = Cfg::kPitch;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -62,7 +70,7 @@ qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kSkBN);
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), Cfg::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -117,7 +125,8 @@ qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0 && active) {
-      constexpr uint32_t idesc = make_idesc_f16(Io<T>::kFmt, /*a_mn=*/0, /*b_mn=*/1, BM, kSkBN);
+      constexpr uint32_t idesc = make_idesc_f16(Io<T>::kFmt, /*a_mn=*/0, /*b_mn=*/1, BM, 256);
+      constexpr uint32_t idesc_tail = make_idesc_f16(Io<T>::kFmt, /*a_mn=*/0, /*b_mn=*/1, BM, 128);
       uint32_t phase = 0;
       bool ok = true;
       for (int i = 0; i < nk && ok; ++i) {
@@ -133,6 +142,10 @@ qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           const uint64_t adesc = make_smem_desc(sa + kk * 32, 0, 1024);
           const uint64_t bdesc = make_smem_desc(sb + kk * 2048, kBBlockBytes, 1024);
           umma_ss(tmem_base, adesc, bdesc, idesc, (i | kk) != 0 ? 1u : 0u);
+          if constexpr (BN == 384) {           // columns 256-383: the stage's fifth and sixth weight blocks
+            const uint64_t bdesc2 = make_smem_desc(sb + 4 * kBBlockBytes + kk * 2048, kBBlockBytes, 1024);
+            umma_ss(tmem_base + 256, adesc, bdesc2, idesc_tail, (i | kk) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(empty_bar(stage));
       }
@@ -185,56 +198,62 @@ qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   for (int r = 0; r < n_split; ++r)
     all_parts = all_parts && reinterpret_cast<volatile uint32_t*>(smem_gen + kSkStages * kStageBytes + 128)[r] != 0u;
   if (rank == 0 && all_parts) {
+    // a task = 64 columns of one row (a head of 64, or half a head of 128: the two halves sit in neighbouring lanes)
     const Seg& sg = p.seg[seg];
-    const int row = threadIdx.x >> 2, cq = threadIdx.x & 3;
-    const int col0 = n_tile * kSkBN + cq * 64;           // first of this thread's 64 columns within the segment
-    const bool live = row < p.rows && col0 < sg.n;
-    float v[64];
+    constexpr int kUnits = kSkBN / 64;
+    const int n_tasks = rows_pad * kUnits;
+#pragma unroll 1
+    for (int task = threadIdx.x; task < ((n_tasks + 31) & ~31); task += kSkThreads) {
+      const int row = task / kUnits, unit = task - row * kUnits;
+      const int col0 = n_tile * kSkBN + unit * 64;         // first of the task's columns within the segment
+      const bool live = task < n_tasks && row < p.rows && col0 < sg.n;
+      float v[64];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = 0.f;
-    if (live) {
-      const float* part = reinterpret_cast<const float*>(smem_gen) + row * kSkPitch + cq * 64;
-      for (int r = 0; r < n_split; ++r) {
+      for (int i = 0; i < 64; ++i) v[i] = 0.f;
+      if (live) {
+        const float* part = reinterpret_cast<const float*>(smem_gen) + row * kSkPitch + unit * 64;
+        for (int r = 0; r < n_split; ++r) {
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          const float4 f = *reinterpret_cast<const float4*>(part + r * rows_pad * kSkPitch + i);
-          v[i] += f.x; v[i + 1] += f.y; v[i + 2] += f.z; v[i + 3] += f.w;
+          for (int i = 0; i < 64; i += 4) {
+            const float4 f = *reinterpret_cast<const float4*>(part + r * rows_pad * kSkPitch + i);
+            v[i] += f.x; v[i + 1] += f.y; v[i + 2] += f.z; v[i + 3] += f.w;
+          }
         }
       }
-    }
-    const float rscale = (live && p.row_scale != nullptr) ? __ldg(p.row_scale + row) : 1.0f;
-    float rs = rscale;
-    if (sg.norm) {
-      float ss = 0.f;
+      const float rscale = (live && p.row_scale != nullptr) ? __ldg(p.row_scale + row) : 1.0f;
+      float rs = rscale;
+      if (sg.norm) {
+        float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float x = v[i] * rscale;
-        ss = fmaf(x, x, ss);
-      }
-      if (p.D == 128) ss += __shfl_xor_sync(0xffffffffu, ss, 1);       // the head's other 64 columns
-      rs = rscale * rsqrtf(ss / static_cast<float>(p.D) + p.qk_eps);
-    }
-    if (live) {
-      const int b = row / p.rows_per_batch, s = row - b * p.rows_per_batch;
-      const int h = col0 / p.D, d0 = col0 - h * p.D;
-      T* out = static_cast<T*>(sg.out) + static_cast<long long>(b) * sg.stride_b +
-               static_cast<long long>(sg.row_off + s) * sg.stride_s + static_cast<long long>(h) * sg.stride_h + d0;
-#pragma unroll
-      for (int i = 0; i < 64; i += 8) {
-        float f[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = v[i + j] * rs;
-        if (sg.gamma != nullptr) {
-          const uint4 g = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(sg.gamma) + d0 + i));
-          const float2 g0 = Io<T>::unpack2(g.x), g1 = Io<T>::unpack2(g.y);
-          const float2 g2 = Io<T>::unpack2(g.z), g3 = Io<T>::unpack2(g.w);
-          f[0] *= g0.x; f[1] *= g0.y; f[2] *= g1.x; f[3] *= g1.y;
-          f[4] *= g2.x; f[5] *= g2.y; f[6] *= g3.x; f[7] *= g3.y;
+        for (int i = 0; i < 64; ++i) {
+          const float x = v[i] * rscale;
+          ss = fmaf(x, x, ss);
         }
-        uint4 o;
-        o.x = Io<T>::pack2(f[0], f[1]); o.y = Io<T>::pack2(f[2], f[3]);
-        o.z = Io<T>::pack2(f[4], f[5]); o.w = Io<T>::pack2(f[6], f[7]);
-        *reinterpret_cast<uint4*>(out + i) = o;
+        if (p.D == 128) ss += __shfl_xor_sync(0xffffffffu, ss, 1);       // the head's other 64 columns
+        rs = rscale * rsqrtf(ss / static_cast<float>(p.D) + p.qk_eps);
+      }
+      if (live) {
+        const int b = row / p.rows_per_batch, s = row - b * p.rows_per_batch;
+        const int h = col0 / p.D, d0 = col0 - h * p.D;
+        T* out = static_cast<T*>(sg.out) + static_cast<long long>(b) * sg.stride_b +
+                 static_cast<long long>(sg.row_off + s) * sg.stride_s + static_cast<long long>(h) * sg.stride_h + d0;
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = v[i + j] * rs;
+          if (sg.gamma != nullptr) {
+            const uint4 g = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(sg.gamma) + d0 + i));
+            const float2 g0 = Io<T>::unpack2(g.x), g1 = Io<T>::unpack2(g.y);
+            const float2 g2 = Io<T>::unpack2(g.z), g3 = Io<T>::unpack2(g.w);
+            f[0] *= g0.x; f[1] *= g0.y; f[2] *= g1.x; f[3] *= g1.y;
+            f[4] *= g2.x; f[5] *= g2.y; f[6] *= g3.x; f[7] *= g3.y;
+          }
+          uint4 o;
+          o.x = Io<T>::pack2(f[0], f[1]); o.y = Io<T>::pack2(f[2], f[3]);
+          o.z = Io<T>::pack2(f[4], f[5]); o.w = Io<T>::pack2(f[6], f[7]);
+          *reinterpret_cast<uint4*>(out + i) = o;
+        }
       }
     }
   }
@@ -243,22 +262,24 @@ qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kSkBN);
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
 
-// rows of x a launch of this kernel can take, and the splits it may try (the launcher asks the device how many clusters
-// of each size it can hold at once)
+// rows of x a launch of this kernel can take; for a tile width, the tiles of the three segments and the largest split
+// the shape allows (the launcher asks the device how many clusters of each size it can hold at once)
+template <int BN>
 inline bool splitk_shape_ok(const TrnProjArgs& a, int* rows_pad_out, int* tiles_out, int* max_split_out) {
+  using Cfg = SkCfg<BN>;
   const long long rows = static_cast<long long>(a.B) * a.M;
   if (rows > kSkARows || (a.D != 64 && a.D != 128)) return false;
   const int rows_pad = rows <= 16 ? 16 : 32;
   const int k_steps = (a.N + BK - 1) / BK;
   int ns = kSkMaxSplit;
   // at least one ring pass of contraction per CTA, parts that fit in rank 0's ring
-  while (ns > 1 && (k_steps < kSkStages * ns || ns * rows_pad * kSkPitch * 4 > kSkStages * kSkStageBytes)) --ns;
+  while (ns > 1 && (k_steps < Cfg::kStages * ns || ns * rows_pad * Cfg::kPitch * 4 > Cfg::kRingBytes)) --ns;
   *rows_pad_out = rows_pad;
-  *tiles_out = (a.Hq * a.D + kSkBN - 1) / kSkBN + 2 * ((a.Hkv * a.D + kSkBN - 1) / kSkBN);
+  *tiles_out = (a.Hq * a.D + BN - 1) / BN + 2 * ((a.Hkv * a.D + BN - 1) / BN);
   *max_split_out = ns;
   return ns > 1;
 }
