@@ -23,9 +23,17 @@
 namespace trn {
 namespace {
 
-constexpr int kAsThreads = 128;
-constexpr int kAsKeys = 32;          // keys per chunk
+// Four warps, 32-key chunks, two stages.  Eight warps with 16-key chunks (two or three stages), eight warps with 32-key
+// chunks and four warps with 16-key chunks in a four-deep ring were A/B'd in one process and came out within the timer's
+// resolution of this layout on every shape tried (Llama M16 / P1024 11.3-12.1 us warm, 18.5 us L2-flushed for all): the
+// key loop is bound by the warp-level MMA rate of the SM (96 mma.m16n8k16 per 32-key chunk with the two-part p), not by
+// how the chunks are dealt out.
+constexpr int kAsWarps = 4;
+constexpr int kAsThreads = 32 * kAsWarps;
+constexpr int kAsKeys = 32;                   // keys per chunk: 16 or 32
 constexpr int kAsStages = 2;
+constexpr int kAsNB = kAsKeys / 8;            // 8-key score blocks per chunk
+constexpr int kAsTPR = kAsThreads / 16;       // threads per row in the merges
 constexpr int kAsMaxSplits = 8;
 
 template <int D>
@@ -33,12 +41,12 @@ struct AsSmem {
   static constexpr int kPitch = D * 2 + 16;                    // bytes per staged key row: conflict-free ldmatrix
   static constexpr int kPanel = kAsKeys * kPitch;              // one [32 x D] panel of k or v
   static constexpr int kWarpRing = kAsStages * 2 * kPanel;
-  static constexpr int kRingBytes = 4 * kWarpRing;
-  // after the key loop the ring is dead: the four warps' partials [4][16][kRow] fp32, then rank 0's exchange area for
+  static constexpr int kRingBytes = kAsWarps * kWarpRing;
+  // after the key loop the ring is dead: the warps' partials [warps][16][kRow] fp32, then rank 0's exchange area for
   // the cluster [8][16][kRow]
   static constexpr int kRow = D + 4;                           // o | max, sum | the perturbed scores' max, sum
   static constexpr int kPart = 0;
-  static constexpr int kXchg = kPart + 4 * 16 * kRow * 4;
+  static constexpr int kXchg = kPart + kAsWarps * 16 * kRow * 4;
   static constexpr int kEpilogue = kXchg + kAsMaxSplits * 16 * kRow * 4;
   static constexpr int kTotal = kRingBytes > kEpilogue ? kRingBytes : kEpilogue;
 };
@@ -103,7 +111,7 @@ attn_small_kernel(const AsParams p) {
   // ---- this warp's chunks of the key range (chunks of 32 keys dealt out evenly to the 4 * n_splits warps)
   const int kv_end = p.causal ? min(p.L, p.P + p.M) : p.L;       // keys any of the queries can see
   const int total_chunks = (kv_end + kAsKeys - 1) / kAsKeys;
-  const int n_warps = 4 * p.n_splits, wi = static_cast<int>(rank) * 4 + warp;
+  const int n_warps = kAsWarps * p.n_splits, wi = static_cast<int>(rank) * kAsWarps + warp;
   const int chunk_lo = total_chunks * wi / n_warps, chunk_hi = total_chunks * (wi + 1) / n_warps;
   const int n_chunks = chunk_hi - chunk_lo;
   const T* kb = static_cast<const T*>(p.k) + b * p.k_sb + kvh * p.k_sh;
@@ -156,18 +164,21 @@ attn_small_kernel(const AsParams p) {
     }
   }
 
-  if (n_chunks > 0) load_stage(0);
-  cp_async_commit();
+#pragma unroll
+  for (int c = 0; c < kAsStages - 1; ++c) {
+    if (c < n_chunks) load_stage(c);
+    cp_async_commit();
+  }
   for (int chunk = 0; chunk < n_chunks; ++chunk) {
-    if (chunk + 1 < n_chunks) load_stage(chunk + 1);
+    if (chunk + kAsStages - 1 < n_chunks) load_stage(chunk + kAsStages - 1);
     cp_async_commit();
     const int s = chunk % kAsStages;
     const int key0 = (chunk_lo + chunk) * kAsKeys;
     // noise of this thread's 16 scores, requested before the wait for the chunk's k / v
-    float gz[4][4];
+    float gz[kAsNB][4];
     if constexpr (kPert) {
 #pragma unroll
-      for (int nb = 0; nb < 4; ++nb) {
+      for (int nb = 0; nb < kAsNB; ++nb) {
         const int key = key0 + nb * 8 + 2 * t;
         if (p.noise.mode == TRN_NOISE_TENSOR && p.noise_pair_ok && key + 1 < p.L) {
           const float2 a = Io<T>::unpack2(__ldg(reinterpret_cast<const uint32_t*>(nz_lo + key)));
@@ -183,18 +194,18 @@ attn_small_kernel(const AsParams p) {
         }
       }
     }
-    cp_async_wait<1>();
+    cp_async_wait<kAsStages - 1>();
     __syncwarp();
     // ---- s = q k^T for 32 keys: four 8-key blocks
-    float sacc[4][4];
+    float sacc[kAsNB][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < kAsNB; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) sacc[i][j] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
-      for (int n2 = 0; n2 < 2; ++n2) {
+      for (int n2 = 0; n2 < kAsNB / 2; ++n2) {
         // matrices: (keys n2*16 .. +7, d ks*16 .. +7), (same keys, d + 8), (keys + 8, d), (keys + 8, d + 8)
         const int key = n2 * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
         const int dd = ks * 16 + ((lane >> 3) & 1) * 8;
@@ -208,10 +219,10 @@ attn_small_kernel(const AsParams p) {
     }
     if constexpr (kPert) {
       // ---- perturbed scores: online log-sum-exp, optional write-out
-      float tl[4][2], th[4][2];
+      float tl[kAsNB][2], th[kAsNB][2];
       float c_lo = -INFINITY, c_hi = -INFINITY;
 #pragma unroll
-      for (int nb = 0; nb < 4; ++nb) {
+      for (int nb = 0; nb < kAsNB; ++nb) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = key0 + nb * 8 + 2 * t + e;
@@ -229,7 +240,7 @@ attn_small_kernel(const AsParams p) {
       const float u_lo = (n_lo == -INFINITY) ? 0.f : n_lo, u_hi = (n_hi == -INFINITY) ? 0.f : n_hi;
       float a_lo = 0.f, a_hi = 0.f;
 #pragma unroll
-      for (int nb = 0; nb < 4; ++nb) {
+      for (int nb = 0; nb < kAsNB; ++nb) {
         a_lo += ex2_approx(tl[nb][0] - u_lo) + ex2_approx(tl[nb][1] - u_lo);
         a_hi += ex2_approx(th[nb][0] - u_hi) + ex2_approx(th[nb][1] - u_hi);
       }
@@ -240,7 +251,7 @@ attn_small_kernel(const AsParams p) {
     // ---- online softmax on the accumulators (log2 domain); invisible keys -> -inf
     float mb_lo = -INFINITY, mb_hi = -INFINITY;
 #pragma unroll
-    for (int nb = 0; nb < 4; ++nb) {
+    for (int nb = 0; nb < kAsNB; ++nb) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int key = key0 + nb * 8 + 2 * t + e;
@@ -261,9 +272,9 @@ attn_small_kernel(const AsParams p) {
     const float al_lo = ex2_approx(m_lo - use_lo), al_hi = ex2_approx(m_hi - use_hi);     // 0 while m = -inf
     m_lo = mn_lo; m_hi = mn_hi;
     float sum_lo = 0.f, sum_hi = 0.f;
-    uint32_t p_hi[4][2], p_lo[4][2];                 // per 8-key block: rows g / g + 8, as packed pairs (hi and lo parts)
+    uint32_t p_hi[kAsNB][2], p_lo[kAsNB][2];                 // per 8-key block: rows g / g + 8, as packed pairs (hi and lo parts)
 #pragma unroll
-    for (int nb = 0; nb < 4; ++nb) {
+    for (int nb = 0; nb < kAsNB; ++nb) {
       const float a0 = ex2_approx(sacc[nb][0] - use_lo), a1 = ex2_approx(sacc[nb][1] - use_lo);
       const float c0 = ex2_approx(sacc[nb][2] - use_hi), c1 = ex2_approx(sacc[nb][3] - use_hi);
       sum_lo += a0 + a1;
@@ -285,7 +296,7 @@ attn_small_kernel(const AsParams p) {
     }
     // ---- o += p v: two k steps of 16 keys; p's accumulator layout is the A fragment's
 #pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
+    for (int kk = 0; kk < kAsKeys / 16; ++kk) {
       const uint32_t ah[4] = {p_hi[2 * kk][0], p_hi[2 * kk][1], p_hi[2 * kk + 1][0], p_hi[2 * kk + 1][1]};
       const uint32_t al[4] = {p_lo[2 * kk][0], p_lo[2 * kk][1], p_lo[2 * kk + 1][0], p_lo[2 * kk + 1][1]};
 #pragma unroll
@@ -329,8 +340,8 @@ attn_small_kernel(const AsParams p) {
   }
   __syncthreads();
   // thread = (row, D / 8 columns): merge `n` partials laid out [n][16][kRow] in fixed order -> (o, max, sum) of the row
-  const int row = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * (D / 8);
-  constexpr int CW = D / 8;
+  constexpr int CW = D / kAsTPR;
+  const int row = threadIdx.x / kAsTPR, c0 = (threadIdx.x % kAsTPR) * CW;
   float acc[CW], mx, tot, mx2 = -INFINITY, tot2 = 0.f;
   auto merge = [&](const float* src, int n) {
     if constexpr (kPert) {
@@ -356,13 +367,13 @@ attn_small_kernel(const AsParams p) {
       for (int c = 0; c < CW; ++c) acc[c] = fmaf(w, src[(i * 16 + row) * SM::kRow + c0 + c], acc[c]);
     }
   };
-  merge(part, 4);
+  merge(part, kAsWarps);
   if (p.n_splits > 1) {
     cluster_sync_all_relaxed();        // every CTA of the cluster is past its ring: rank 0's exchange area may be written
     const uint32_t slot = map_to_rank(smem_base + SM::kXchg, 0) + rank * (16 * SM::kRow * 4);
 #pragma unroll
     for (int c = 0; c < CW; c += 2) st_cluster_f2(slot + (row * SM::kRow + c0 + c) * 4, acc[c], acc[c + 1]);
-    if ((threadIdx.x & 7) == 0) {
+    if ((threadIdx.x % kAsTPR) == 0) {
       st_cluster_f2(slot + (row * SM::kRow + D) * 4, mx, tot);
       if constexpr (kPert) st_cluster_f2(slot + (row * SM::kRow + D + 2) * 4, mx2, tot2);
     }
@@ -374,17 +385,26 @@ attn_small_kernel(const AsParams p) {
     const int hd = row / p.M, i = row - hd * p.M, h = h0 + hd;
     const float inv = tot > 0.f ? 1.0f / tot : 0.f;
     T* dst = static_cast<T*>(p.o) + b * p.o_sb + static_cast<long long>(i) * p.o_ss + h * p.o_sh + c0;
+    if constexpr (CW % 8 == 0) {
 #pragma unroll
-    for (int c = 0; c < CW; c += 8) {
-      uint4 v;
-      v.x = Io<T>::pack2(acc[c] * inv, acc[c + 1] * inv); v.y = Io<T>::pack2(acc[c + 2] * inv, acc[c + 3] * inv);
-      v.z = Io<T>::pack2(acc[c + 4] * inv, acc[c + 5] * inv); v.w = Io<T>::pack2(acc[c + 6] * inv, acc[c + 7] * inv);
-      *reinterpret_cast<uint4*>(dst + c) = v;
+      for (int c = 0; c < CW; c += 8) {
+        uint4 v;
+        v.x = Io<T>::pack2(acc[c] * inv, acc[c + 1] * inv); v.y = Io<T>::pack2(acc[c + 2] * inv, acc[c + 3] * inv);
+        v.z = Io<T>::pack2(acc[c + 4] * inv, acc[c + 5] * inv); v.w = Io<T>::pack2(acc[c + 6] * inv, acc[c + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + c) = v;
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < CW; c += 4) {
+        uint2 v;
+        v.x = Io<T>::pack2(acc[c] * inv, acc[c + 1] * inv); v.y = Io<T>::pack2(acc[c + 2] * inv, acc[c + 3] * inv);
+        *reinterpret_cast<uint2*>(dst + c) = v;
+      }
     }
-    if (p.lse != nullptr && (threadIdx.x & 7) == 0)
+    if (p.lse != nullptr && (threadIdx.x % kAsTPR) == 0)
       p.lse[(static_cast<long long>(b) * p.Hq + h) * p.M + i] = mx + log2f(tot);
     if constexpr (kPert) {
-      if ((threadIdx.x & 7) == 0) p.lse_pert[(static_cast<long long>(b) * p.Hq + h) * p.M + i] = mx2 + log2f(tot2);
+      if ((threadIdx.x % kAsTPR) == 0) p.lse_pert[(static_cast<long long>(b) * p.Hq + h) * p.M + i] = mx2 + log2f(tot2);
     }
   }
 }
@@ -427,7 +447,7 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   const long long heads = static_cast<long long>(a.B) * (a.Hq / p.pack);
   const int chunks = (p.L + kAsKeys - 1) / kAsKeys;
   int ns = kAsMaxSplits;
-  while (ns > 1 && (heads * ns > ds.sm_count || chunks < 8 * ns)) ns >>= 1;
+  while (ns > 1 && (heads * ns > ds.sm_count || chunks < 2 * kAsWarps * ns)) ns >>= 1;
   p.n_splits = ns;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(heads * ns), 1, 1);
