@@ -475,10 +475,22 @@ int trinity_attn_block(const TrnBlockArgs* a, void* cuda_stream) {
     at.noise_bh0 = a->noise_bh0;
     at.lse_pert = lse_pert;
   }
-  rc = launch_attention(at, st, *ds);
+  // At most 16 queries per head: the statistics ride in the attention launch (every score of a head is on chip when
+  // its rows' log-sum-exp is known), whatever keep_scores says; nothing is kept and no second launch follows.
+  AttnFusedStats fstats{};
+  if (stats) {
+    fstats.sum_p = a->sum_p;
+    fstats.sum_p2 = (a->variant == TRN_ROCO) ? a->sum_p2 : nullptr;
+    fstats.stats_fp32 = a->stats_fp32;
+    if (attn_small_stats_applies(at, ds->sm_count)) {
+      at.scores = nullptr;
+      at.score_pitch = 0;
+    }
+  }
+  rc = launch_attention(at, st, *ds, stats ? &fstats : nullptr);
   if (rc != TRN_OK) return rc;
 
-  if (stats) {
+  if (stats && !fstats.done) {
     const float* lse_for_stats = lse;
     int noise_mode = TRN_NOISE_NONE;
     if (a->variant == TRN_KEYFORMER) {

@@ -1198,7 +1198,7 @@ size_t attn_split_workspace(int B, int M, int P, int Hq, int Hkv, int D, int sm_
   return split_bytes(n, static_cast<long long>(B) * Hq * M, D, true);
 }
 
-int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
+int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds, AttnFusedStats* fstats) {
   if (a.B <= 0 || a.M <= 0 || a.P < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.Hq % a.Hkv != 0) return TRN_E_SHAPE;
   if (a.D != 64 && a.D != 128) return TRN_E_SHAPE;
   if (!(a.scale > 0.f)) return TRN_E_SHAPE;
@@ -1221,7 +1221,15 @@ int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& d
     if (a.score_pitch < a.P + a.M || (a.score_pitch & 31) != 0 || !aligned16(a.scores)) return TRN_E_SHAPE;
   }
   if (a.dtype != TRN_BF16 && a.dtype != TRN_FP16) return TRN_E_DTYPE;
-  if (attn_small_applies(a)) return launch_attn_small(a, st, ds);
+  if (fstats != nullptr) fstats->done = 0;
+  if (attn_small_applies(a)) {
+    if (fstats != nullptr && fstats->sum_p != nullptr && attn_small_stats_applies(a, ds.sm_count)) {
+      const int rc = launch_attn_small(a, st, ds, fstats);
+      if (rc == TRN_OK) fstats->done = 1;
+      return rc;
+    }
+    return launch_attn_small(a, st, ds);
+  }
   if (a.dtype == TRN_BF16) return launch_typed<__nv_bfloat16>(a, st, ds);
   return launch_typed<__half>(a, st, ds);
 }

@@ -32,6 +32,8 @@ constexpr int kAsWarps = 4;
 constexpr int kAsThreads = 32 * kAsWarps;
 constexpr int kAsKeys = 32;                   // keys per chunk: 16 or 32
 constexpr int kAsStages = 2;
+constexpr int kAsKeepChunks = 5;              // chunks of scores a warp can keep for the fused statistics
+constexpr int kAsKeepPitch = kAsKeepChunks * kAsKeys + 8;   // +8 floats: rows g = 0..7 of a float2 store spread over the banks
 constexpr int kAsNB = kAsKeys / 8;            // 8-key score blocks per chunk
 constexpr int kAsTPR = kAsThreads / 16;       // threads per row in the merges
 constexpr int kAsMaxSplits = 8;
@@ -49,6 +51,11 @@ struct AsSmem {
   static constexpr int kXchg = kPart + kAsWarps * 16 * kRow * 4;
   static constexpr int kEpilogue = kXchg + kAsMaxSplits * 16 * kRow * 4;
   static constexpr int kTotal = kRingBytes > kEpilogue ? kRingBytes : kEpilogue;
+  // launches that also sum the per-key statistics keep every score of the CTA until the rows' log-sum-exp is known:
+  // [warp][16 rows][kKeepPitch] fp32 behind everything else, then the 16 log-sum-exps rank 0 hands to every rank
+  static constexpr int kKeep = (kTotal + 127) & ~127;
+  static constexpr int kLseBcast = kKeep + kAsWarps * 16 * kAsKeepPitch * 4;
+  static constexpr int kTotalStats = kLseBcast + 16 * 4;
 };
 
 struct AsParams {
@@ -67,6 +74,11 @@ struct AsParams {
   float* lse_pert;             // MODE 2: [B, Hq, M]
   float* scores;               // optional [B, Hq, M, score_pitch]
   long long score_pitch;
+  // MODE 2 / 3, optional: per-key sums over the queries of p = 2^(t - lse) (and of p^2) in the same launch, t = the
+  // perturbed (MODE 2) or plain (MODE 3) scores, [B, Hq, L] fp32 or T (the statistics of trinity_attn_colstats)
+  void* sum_p;
+  void* sum_p2;
+  int stats_fp32;
 };
 
 // HILO: p enters p v as two 16-bit parts (hi + lo, the library's default accuracy); false: one part (single_p callers)
@@ -157,6 +169,8 @@ attn_small_kernel(const AsParams p) {
       nz_hi = static_cast<const T*>(p.noise.ptr) + b * p.noise.sb + hq_hi * p.noise.sh + i_hi * p.noise.si;
     }
   }
+  const bool fuse_stats = MODE != 0 && p.sum_p != nullptr;
+  float* keep = reinterpret_cast<float*>(as_smem + SM::kKeep) + warp * 16 * kAsKeepPitch;
   if constexpr (MODE != 0) {
     if (p.scores != nullptr) {
       if (row_lo) sc_lo = p.scores + ((static_cast<long long>(b) * p.Hq + hq_lo) * p.M + i_lo) * p.score_pitch;
@@ -233,6 +247,10 @@ attn_small_kernel(const AsParams p) {
         }
         if (sc_lo != nullptr) *reinterpret_cast<float2*>(sc_lo + key0 + nb * 8 + 2 * t) = make_float2(tl[nb][0], tl[nb][1]);
         if (sc_hi != nullptr) *reinterpret_cast<float2*>(sc_hi + key0 + nb * 8 + 2 * t) = make_float2(th[nb][0], th[nb][1]);
+        if (fuse_stats) {
+          *reinterpret_cast<float2*>(keep + g * kAsKeepPitch + chunk * kAsKeys + nb * 8 + 2 * t) = make_float2(tl[nb][0], tl[nb][1]);
+          *reinterpret_cast<float2*>(keep + (g + 8) * kAsKeepPitch + chunk * kAsKeys + nb * 8 + 2 * t) = make_float2(th[nb][0], th[nb][1]);
+        }
       }
       c_lo = fmaxf(c_lo, __shfl_xor_sync(0xffffffffu, c_lo, 1)); c_lo = fmaxf(c_lo, __shfl_xor_sync(0xffffffffu, c_lo, 2));
       c_hi = fmaxf(c_hi, __shfl_xor_sync(0xffffffffu, c_hi, 1)); c_hi = fmaxf(c_hi, __shfl_xor_sync(0xffffffffu, c_hi, 2));
@@ -263,6 +281,10 @@ attn_small_kernel(const AsParams p) {
       if constexpr (MODE == 3) {
         if (sc_lo != nullptr) *reinterpret_cast<float2*>(sc_lo + key0 + nb * 8 + 2 * t) = make_float2(sacc[nb][0], sacc[nb][1]);
         if (sc_hi != nullptr) *reinterpret_cast<float2*>(sc_hi + key0 + nb * 8 + 2 * t) = make_float2(sacc[nb][2], sacc[nb][3]);
+        if (fuse_stats) {
+          *reinterpret_cast<float2*>(keep + g * kAsKeepPitch + chunk * kAsKeys + nb * 8 + 2 * t) = make_float2(sacc[nb][0], sacc[nb][1]);
+          *reinterpret_cast<float2*>(keep + (g + 8) * kAsKeepPitch + chunk * kAsKeys + nb * 8 + 2 * t) = make_float2(sacc[nb][2], sacc[nb][3]);
+        }
       }
     }
     mb_lo = fmaxf(mb_lo, __shfl_xor_sync(0xffffffffu, mb_lo, 1)); mb_lo = fmaxf(mb_lo, __shfl_xor_sync(0xffffffffu, mb_lo, 2));
@@ -378,10 +400,17 @@ attn_small_kernel(const AsParams p) {
       if constexpr (kPert) st_cluster_f2(slot + (row * SM::kRow + D + 2) * 4, mx2, tot2);
     }
     cluster_sync_all();                // the parts of every rank have landed in rank 0
-    if (rank != 0) return;
-    merge(reinterpret_cast<const float*>(as_smem + SM::kXchg), p.n_splits);
+    if (rank != 0 && !fuse_stats) return;
+    if (rank == 0) merge(reinterpret_cast<const float*>(as_smem + SM::kXchg), p.n_splits);
   }
-  if (row < n_rows) {
+  if (rank == 0 && fuse_stats && (threadIdx.x % kAsTPR) == 0) {
+    // the log-sum-exp the statistics are taken against (perturbed scores' in MODE 2), to every rank of the cluster
+    const float l = kPert ? mx2 + log2f(tot2) : mx + log2f(tot);
+    for (int r = 0; r < p.n_splits; ++r)
+      st_cluster_u32((p.n_splits > 1 ? map_to_rank(smem_base + SM::kLseBcast, r) : smem_base + SM::kLseBcast) + row * 4,
+                     __float_as_uint(l));
+  }
+  if (rank == 0 && row < n_rows) {
     const int hd = row / p.M, i = row - hd * p.M, h = h0 + hd;
     const float inv = tot > 0.f ? 1.0f / tot : 0.f;
     T* dst = static_cast<T*>(p.o) + b * p.o_sb + static_cast<long long>(i) * p.o_ss + h * p.o_sh + c0;
@@ -407,15 +436,64 @@ attn_small_kernel(const AsParams p) {
       if ((threadIdx.x % kAsTPR) == 0) p.lse_pert[(static_cast<long long>(b) * p.Hq + h) * p.M + i] = mx2 + log2f(tot2);
     }
   }
+  if constexpr (MODE != 0) {
+    if (fuse_stats) {
+      // ---- per-key statistics of this warp's keys (the launcher fuses only unpacked heads: row = query, h0 = head):
+      // thread = key, queries in ascending order, the arithmetic of colstats_from_scores_kernel on the same numbers
+      if (p.n_splits > 1) cluster_sync_all(); else __syncthreads();
+      const float* lse_row = reinterpret_cast<const float*>(as_smem + SM::kLseBcast);
+      const long long out0 = (static_cast<long long>(b) * p.Hq + h0) * p.L;
+      const int first_query_off = p.causal ? p.P : p.L;
+      for (int kk = lane; kk < n_chunks * kAsKeys; kk += 32) {
+        const int key = chunk_lo * kAsKeys + kk;
+        if (key >= p.L) break;
+        float a1 = 0.f, a2 = 0.f;
+        for (int i = max(0, key - first_query_off); i < p.M; ++i) {
+          const float pr = ex2_approx(keep[i * kAsKeepPitch + kk] - lse_row[i]);
+          a1 += pr;
+          a2 = fmaf(pr, pr, a2);
+        }
+        if (p.stats_fp32) {
+          static_cast<float*>(p.sum_p)[out0 + key] = a1;
+          if (p.sum_p2 != nullptr) static_cast<float*>(p.sum_p2)[out0 + key] = a2;
+        } else {
+          static_cast<T*>(p.sum_p)[out0 + key] = Io<T>::from_f(a1);
+          if (p.sum_p2 != nullptr) static_cast<T*>(p.sum_p2)[out0 + key] = Io<T>::from_f(a2);
+        }
+      }
+    }
+  }
+}
+
+// grouped-query heads of one kv head share the CTA's 16 rows while they fit (decode: M = 1 packs 16 heads)
+int pack_of(const TrnAttnArgs& a) {
+  const int group = a.Hq / a.Hkv;
+  for (int c = group; c >= 1; --c)
+    if (group % c == 0 && c * a.M <= 16) return c;
+  return 1;
+}
+// CTAs per unit (= cluster size): fill the SMs once, keep every warp at least two chunks of keys
+int splits_of(const TrnAttnArgs& a, int pack, int sm_count) {
+  const long long units = static_cast<long long>(a.B) * (a.Hq / pack);
+  const int chunks = (a.P + a.M + kAsKeys - 1) / kAsKeys;
+  int ns = kAsMaxSplits;
+  while (ns > 1 && (units * ns > sm_count || chunks < 2 * kAsWarps * ns)) ns >>= 1;
+  return ns;
 }
 
 template <typename T, int D, bool HILO, int MODE>
-int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
+int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds, const AttnFusedStats* fs = nullptr) {
   using SM = AsSmem<D>;
   auto kern = attn_small_kernel<T, D, HILO, MODE>;
-  const int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotal, ds.device);
+  const int smem = (fs != nullptr && MODE != 0) ? SM::kTotalStats : SM::kTotal;
+  const int rc = ensure_dyn_smem(reinterpret_cast<const void*>(kern), SM::kTotalStats, ds.device);
   if (rc != TRN_OK) return rc;
   AsParams p{};
+  if (fs != nullptr && MODE != 0) {
+    p.sum_p = fs->sum_p;
+    p.sum_p2 = fs->sum_p2;
+    p.stats_fp32 = fs->stats_fp32;
+  }
   p.q = a.q.ptr; p.k = a.k_cache.ptr; p.v = a.v_cache.ptr; p.o = a.o.ptr;
   p.q_sb = a.q.stride_b; p.q_ss = a.q.stride_s; p.q_sh = a.q.stride_h;
   p.k_sb = a.k_cache.stride_b; p.k_ss = a.k_cache.stride_s; p.k_sh = a.k_cache.stride_h;
@@ -439,20 +517,14 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
   p.lse_pert = a.lse_pert;
   p.scores = a.scores;
   p.score_pitch = a.score_pitch;
-  // grouped-query heads of one kv head share the CTA's 16 rows while they fit (decode: M = 1 packs 16 heads)
-  p.pack = 1;
-  for (int c = p.group; c >= 1; --c)
-    if (p.group % c == 0 && c * a.M <= 16) { p.pack = c; break; }
-  // CTAs per unit (= cluster size): fill the SMs once, keep every warp at least two chunks of keys
+  p.pack = pack_of(a);
   const long long heads = static_cast<long long>(a.B) * (a.Hq / p.pack);
-  const int chunks = (p.L + kAsKeys - 1) / kAsKeys;
-  int ns = kAsMaxSplits;
-  while (ns > 1 && (heads * ns > ds.sm_count || chunks < 2 * kAsWarps * ns)) ns >>= 1;
+  const int ns = splits_of(a, p.pack, ds.sm_count);
   p.n_splits = ns;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(heads * ns), 1, 1);
   cfg.blockDim = dim3(kAsThreads, 1, 1);
-  cfg.dynamicSmemBytes = SM::kTotal;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -468,9 +540,9 @@ int launch_inst(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
 }
 
 template <typename T, int D>
-int launch_mode(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
-  if (a.noise_mode != TRN_NOISE_NONE) return launch_inst<T, D, true, 2>(a, st, ds);
-  if (a.scores != nullptr) return launch_inst<T, D, true, 3>(a, st, ds);
+int launch_mode(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds, const AttnFusedStats* fs) {
+  if (a.noise_mode != TRN_NOISE_NONE) return launch_inst<T, D, true, 2>(a, st, ds, fs);
+  if (a.scores != nullptr || fs != nullptr) return launch_inst<T, D, true, 3>(a, st, ds, fs);
   return a.single_p == 0 ? launch_inst<T, D, true, 0>(a, st, ds) : launch_inst<T, D, false, 0>(a, st, ds);
 }
 
@@ -483,9 +555,21 @@ bool attn_small_applies(const TrnAttnArgs& a) {
   return a.M <= 16 && (a.D == 64 || a.D == 128) && static_cast<long long>(a.B) * a.Hq <= 0x3fffffffLL;
 }
 
-int launch_attn_small(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds) {
-  if (a.dtype == TRN_BF16) return a.D == 128 ? launch_mode<__nv_bfloat16, 128>(a, st, ds) : launch_mode<__nv_bfloat16, 64>(a, st, ds);
-  if (a.dtype == TRN_FP16) return a.D == 128 ? launch_mode<__half, 128>(a, st, ds) : launch_mode<__half, 64>(a, st, ds);
+// the statistics can ride along when a row is a query of ONE head (no packed heads) and every warp's share of the keys
+// fits its score area
+bool attn_small_stats_applies(const TrnAttnArgs& a, int sm_count) {
+  if (!attn_small_applies(a)) return false;
+  const int pack = pack_of(a);
+  if (pack != 1) return false;
+  const int ns = splits_of(a, pack, sm_count);
+  const int chunks = (a.P + a.M + kAsKeys - 1) / kAsKeys, warps = kAsWarps * ns;
+  return (chunks + warps - 1) / warps <= kAsKeepChunks;
+}
+
+int launch_attn_small(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds, const AttnFusedStats* fs) {
+  if (a.dtype == TRN_BF16)
+    return a.D == 128 ? launch_mode<__nv_bfloat16, 128>(a, st, ds, fs) : launch_mode<__nv_bfloat16, 64>(a, st, ds, fs);
+  if (a.dtype == TRN_FP16) return a.D == 128 ? launch_mode<__half, 128>(a, st, ds, fs) : launch_mode<__half, 64>(a, st, ds, fs);
   return TRN_E_DTYPE;
 }
 

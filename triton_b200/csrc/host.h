@@ -74,11 +74,22 @@ int launch_gmlp_small(const TrnGmlpArgs& a, cudaStream_t st, const DeviceState& 
 // at most 16 tokens: one latency-oriented launch (lora_small.cu); callers validate the arguments first
 bool lora_small_applies(const TrnLoraArgs& a);
 int launch_lora_small(const TrnLoraArgs& a, cudaStream_t st, const DeviceState& ds);
-int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
-// plain attention with at most 16 queries per head: one latency-oriented launch (attn_small.cu); launch_attention
-// validates the arguments and routes here
+// Per-key statistics a caller would take from the attention pass's scores right afterwards (trinity_attn_colstats on
+// the perturbed scores when the launch carries noise, else on the plain ones).  With `fused` given, launch_attention
+// computes them in the same launch when the shape allows and sets done = 1; otherwise it leaves done = 0 and the caller
+// runs the statistics kernel.
+struct AttnFusedStats {
+  void* sum_p;
+  void* sum_p2;    // or nullptr
+  int stats_fp32;
+  int done;
+};
+int launch_attention(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds, AttnFusedStats* fused = nullptr);
+// attention with at most 16 queries per head: one latency-oriented launch (attn_small.cu); launch_attention validates
+// the arguments and routes here
 bool attn_small_applies(const TrnAttnArgs& a);
-int launch_attn_small(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds);
+bool attn_small_stats_applies(const TrnAttnArgs& a, int sm_count);
+int launch_attn_small(const TrnAttnArgs& a, cudaStream_t st, const DeviceState& ds, const AttnFusedStats* fs = nullptr);
 // split-KV policy of the attention kernel: how many CTAs share one tile pair's key range (1: no split),
 // and the scratch a launch of that shape wants for the partial results (0: it would not split)
 constexpr int kAttnMaxSplits = 8;
