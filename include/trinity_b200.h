@@ -339,7 +339,9 @@ typedef struct {
                       the statistics from memory whenever they fit in 1 GiB — the schedule of the reference's
                       candidates that hold C_exp / C_exp_perturb in memory (TritonGen.py:1007-1042); -1: never keep
                       them, recompute q k^T in a second pass (candidates whose scores live in registers only).
-                      trinity_attn_block_workspace() sizes the workspace for the same choice. */
+                      trinity_attn_block_workspace() sizes the workspace for the same choice.  With at most 16
+                      queries per head (M) and unpacked heads the statistics are summed inside the attention launch
+                      in every setting — the scores never leave the chip — with bitwise the sums of setting 1. */
   int noise_heads; /* as in TrnAttnArgs: slices of a larger KeyFormer problem see the whole problem's noise */
   int noise_bh0;
 } TrnBlockArgs;

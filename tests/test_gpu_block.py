@@ -409,3 +409,43 @@ def test_candidate_structure_selects_the_statistics_schedule(M):
     for k in ("C_out1", "C_out2"):
         assert_parity(outs["recompute"][1][k].cuda().half(), outs["kept"][1][k], f"{k}: recompute vs kept scores", rel_tol=2e-2)
     assert L.kernel_status() == 0
+
+
+@pytest.mark.parametrize("variant,B,M,P,Hq,Hkv,D,dt,causal,stats_dtype", (
+    ("keyformer", 1, 16, 1024, 8, 8, 128, HF, False, torch.float32),     # the reference's shape
+    ("roco", 1, 16, 1024, 6, 6, 64, HF, False, torch.float16),
+    ("keyformer", 2, 9, 300, 4, 4, 64, BF, True, torch.float32),        # causal, ragged, 16-bit io with fp32 sums
+    ("roco", 1, 16, 40, 4, 2, 128, BF, True, torch.bfloat16),           # GQA with 16 queries: heads are not packed
+))
+def test_statistics_summed_inside_the_small_attention_launch_equal_the_two_kernel_path(variant, B, M, P, Hq, Hkv, D, dt,
+                                                                                      causal, stats_dtype):
+    """With at most 16 queries the block sums the per-key statistics inside the attention launch.  The same numbers
+    through the public pieces — attention that keeps its scores, then the statistics kernel on them — agree bit for
+    bit: both add 2^(t - lse) over the queries in ascending order."""
+    scale, tau = D ** -0.5, 1.5
+    t = block_inputs(31, B, M, P, 64, Hq, Hkv, D, dt, variant=variant)
+    torch.manual_seed(32)
+    t["Q"] = torch.randn(B, M, Hq, D).to(dt)
+    r = run_block(variant, t, B=B, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, causal=causal, scale=scale, tau=tau,
+                  stats_dtype=stats_dtype, project=False)
+    L_ = P + M
+    pitch = (L_ + 31) // 32 * 32
+    qv, kv, vv = ops.as_bshd(t["Q"].cuda(), "bshd"), ops.as_bshd(t["K_cache"].cuda(), "bhsd"), ops.as_bshd(t["V_cache"].cuda(), "bhsd")
+    o = torch.zeros(B, M, Hq, D, device="cuda", dtype=dt)
+    lse, lse2 = torch.zeros(B, Hq, M, device="cuda"), torch.zeros(B, Hq, M, device="cuda")
+    sc = torch.full((B, Hq, M, pitch), float("nan"), device="cuda")
+    kw = dict(P=P, causal=causal, scale=scale)
+    sp, sp2 = (torch.zeros(B, Hq, L_, device="cuda", dtype=stats_dtype) for _ in range(2))
+    if variant == "keyformer":
+        ops.attention(qv, kv, vv, o, lse=lse, lse_pert=lse2, scores=sc, noise_mode=L.TRN_NOISE_TENSOR, tau=tau,
+                      noise=t["noise"].cuda(), **kw)
+        ops.attn_colstats(qv, kv, lse2, sp, None, scores=sc, **kw)
+    else:
+        ops.attention(qv, kv, vv, o, lse=lse, scores=sc, **kw)
+        ops.attn_colstats(qv, kv, lse, sp, sp2, scores=sc, **kw)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    assert torch.equal(r["out"], o)
+    assert torch.equal(r["sum_p"], sp)
+    if variant == "roco":
+        assert torch.equal(r["sum_p2"], sp2)
