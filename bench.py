@@ -573,8 +573,8 @@ def run_ours(args, w):
                             "frac": ach / peaks["tflops"], "peak_source": peaks["kind"] + " burst",
                             "traffic": traffic,
                             "traffic_source": None if traffic is None else
-                            "dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch, ncu capture of an "
-                            "earlier build of this kernel (not re-measured in this run)"}
+                            "dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch, ncu capture of this "
+                            "kernel (profiles/prenorm_llama_full_size_kernels.md), not re-measured in this run"}
         for k in kern_flops:
             line[k + "_tflops"] = kern_flops[k] / (kern_us[k] * 1e-6) / 1e12
     if world == 1 and not args.no_cpu:
@@ -588,9 +588,9 @@ def run_ours(args, w):
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the named kernel at the workload's full
 # size, from ncu captures (None where no capture was taken)
 TRAFFIC_BYTES = {
-    ("prenorm_llama", "qkv_gemm"): 409042944 + 178885120,
-    ("prenorm_llama", "attention"): 308813824 + 99281152,
-    "rmsnorm_llama": 134235648 + 79863808,
+    ("prenorm_llama", "qkv_gemm"): 423863808 + 184058112,
+    ("prenorm_llama", "attention"): 297662720 + 102904832,
+    "rmsnorm_llama": 134235392 + 81776128,
 }
 
 
@@ -811,7 +811,9 @@ def run_rmsnorm(args, w):
             "roofline": {"kernel": "rmsnorm_cta_kernel", "bound": "hbm", "achieved": gbs, "peak": peaks["hbm"],
                          "unit": "GB/s", "frac": gbs / peaks["hbm"], "peak_source": peaks["kind"],
                          "traffic": TRAFFIC_BYTES.get(args.workload),
-                         "traffic_source": "ncu capture of an earlier build of this kernel (not re-measured in this run)"}}
+                         "traffic_source": None if TRAFFIC_BYTES.get(args.workload) is None else
+                         "ncu capture of this kernel inside the PreNorm block (profiles/prenorm_llama_full_size_kernels.md), "
+                         "not re-measured in this run"}}
     print(json.dumps(line))
 
 
