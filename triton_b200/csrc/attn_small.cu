@@ -120,7 +120,7 @@ attn_small_kernel(const AsParams p) {
     qa[ks][3] = row_hi ? __ldg(hi + 4 + t) : 0u;
   }
 
-  // ---- this warp's chunks of the key range (chunks of 32 keys dealt out evenly to the 4 * n_splits warps)
+  // ---- this warp's chunks of the key range (chunks of kAsKeys keys dealt out evenly to the kAsWarps * n_splits warps of the cluster)
   const int kv_end = p.causal ? min(p.L, p.P + p.M) : p.L;       // keys any of the queries can see
   const int total_chunks = (kv_end + kAsKeys - 1) / kAsKeys;
   const int n_warps = kAsWarps * p.n_splits, wi = static_cast<int>(rank) * kAsWarps + warp;
