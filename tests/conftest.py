@@ -60,7 +60,7 @@ def parity_errors(got, ref, rel_floor=REL_FLOOR):
 # GPU tests ran, written as JSON lines to PARITY_LOG at the end of the session: the measured errors behind the
 # pass / fail verdicts.  `config` groups records of one benchmark configuration.
 PARITY_RECORDS = []
-PARITY_LOG = os.environ.get("TRINITY_PARITY_LOG", os.path.join(ROOT, "gpurun_out", "parity_errors.jsonl"))
+PARITY_LOG = os.environ.get("TRINITY_PARITY_LOG", os.path.join(ROOT, "test_out", "parity_errors.jsonl"))
 
 
 def record(kind, what, config=None, **fields):
