@@ -57,6 +57,26 @@ qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const uint32_t rank = cluster_ctarank();
   Ctl ctl{p.status, abort_flag};
 
+  // this CTA's tile and contraction range
+  const int tile = static_cast<int>(blockIdx.x) / n_split;
+  const int seg = (tile >= p.seg[2].tile0) ? 2 : (tile >= p.seg[1].tile0 ? 1 : 0);
+  const int n_tile = tile - p.seg[seg].tile0;
+  const CUtensorMap* tm_w = seg == 0 ? &tm_w0 : (seg == 1 ? &tm_w1 : &tm_w2);
+  const int k_steps_all = (p.K + BK - 1) / BK;
+  const int k_lo = k_steps_all * static_cast<int>(rank) / n_split;
+  const int k_hi = k_steps_all * (static_cast<int>(rank) + 1) / n_split;
+  const int nk = k_hi - k_lo;
+  const int first = nk < kSkStages ? nk : kSkStages;      // stages of the first ring fill
+  auto load_w = [&](int i) {
+    const uint32_t sb = smem_base + (i % kSkStages) * kStageBytes + kSkABytes;
+#pragma unroll
+    for (int c = 0; c < kSkBN / 64; ++c)
+      tma_load_2d(sb + c * kBBlockBytes, tm_w, full_bar(i % kSkStages), n_tile * kSkBN + c * 64, (k_lo + i) * BK);
+  };
+  auto load_x = [&](int i) {
+    tma_load_2d(smem_base + (i % kSkStages) * kStageBytes, &tm_x, full_bar(i % kSkStages), (k_lo + i) * BK, 0);
+  };
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSkStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -66,8 +86,19 @@ qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     *abort_flag = 0;
     // an earlier kernel gave up: do no work, but keep every cluster barrier below (the CTAs of a cluster may read
     // different values of the word; none of them may wait for one that left)
-    *skip_flag = *reinterpret_cast<volatile int*>(p.status);
+    const int skip = *reinterpret_cast<volatile int*>(p.status);
+    *skip_flag = skip;
     fence_mbar_init();
+    // The first ring fill's WEIGHT loads go out here, by the thread that has just initialised the barriers: before
+    // the CTA meets (tensor-memory allocation is still under way) and before the wait on the previous kernel.
+    if (skip == 0) {
+      tma_prefetch_desc(tm_w);
+      for (int i = 0; i < first; ++i) {
+        mbar_expect_tx(full_bar(i), kStageBytes);
+        load_w(i);
+      }
+      tma_prefetch_desc(&tm_x);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), Cfg::kTmemCols);
@@ -79,36 +110,10 @@ qkv_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const uint32_t tmem_base = *tmem_ptr_smem;
   const bool active = *skip_flag == 0;
 
-  // this CTA's tile and contraction range
-  const int tile = static_cast<int>(blockIdx.x) / n_split;
-  const int seg = (tile >= p.seg[2].tile0) ? 2 : (tile >= p.seg[1].tile0 ? 1 : 0);
-  const int n_tile = tile - p.seg[seg].tile0;
-  const CUtensorMap* tm_w = seg == 0 ? &tm_w0 : (seg == 1 ? &tm_w1 : &tm_w2);
-  const int k_steps_all = (p.K + BK - 1) / BK;
-  const int k_lo = k_steps_all * static_cast<int>(rank) / n_split;
-  const int k_hi = k_steps_all * (static_cast<int>(rank) + 1) / n_split;
-  const int nk = k_hi - k_lo;
-
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0 && active) {
-      tma_prefetch_desc(&tm_x);
-      tma_prefetch_desc(tm_w);
-      auto load_w = [&](int i) {
-        const uint32_t sb = smem_base + (i % kSkStages) * kStageBytes + kSkABytes;
-#pragma unroll
-        for (int c = 0; c < kSkBN / 64; ++c)
-          tma_load_2d(sb + c * kBBlockBytes, tm_w, full_bar(i % kSkStages), n_tile * kSkBN + c * 64, (k_lo + i) * BK);
-      };
-      auto load_x = [&](int i) {
-        tma_load_2d(smem_base + (i % kSkStages) * kStageBytes, &tm_x, full_bar(i % kSkStages), (k_lo + i) * BK, 0);
-      };
-      // first ring fill: weights now, x once the previous kernel of the stream has finished
-      const int first = nk < kSkStages ? nk : kSkStages;
-      for (int i = 0; i < first; ++i) {
-        mbar_expect_tx(full_bar(i), kStageBytes);
-        load_w(i);
-      }
+      // x once the previous kernel of the stream has finished
       griddep_wait();
       for (int i = 0; i < first; ++i) load_x(i);
       uint32_t phase = 0;                       // parity of the ring pass being waited for
