@@ -449,3 +449,22 @@ def test_statistics_summed_inside_the_small_attention_launch_equal_the_two_kerne
     assert torch.equal(r["sum_p"], sp)
     if variant == "roco":
         assert torch.equal(r["sum_p2"], sp2)
+
+
+@pytest.mark.parametrize("variant,M,P,N,Hq,Hkv,D", (
+    ("prenorm", 16, 1024, 1024, 8, 8, 128),        # split-K projection (weights requested before the dependency wait)
+    ("keyformer", 16, 200, 512, 4, 4, 64),         # + the small attention kernel with the statistics inside
+    ("qknorm", 300, 40, 512, 4, 2, 128),           # persistent projection + tensor-memory attention
+))
+def test_plain_stream_order_gives_the_same_block_as_dependent_launch(variant, M, P, N, Hq, Hkv, D, monkeypatch):
+    """TRINITY_NO_PDL=1 launches every kernel plainly stream-ordered (the library reads the variable per launch):
+    the results equal those of the default, programmatic dependent launch, bit for bit."""
+    t = block_inputs(41, 1, M, P, N, Hq, Hkv, D, HF, variant=variant)
+    kw = dict(B=1, M=M, P=P, Hq=Hq, Hkv=Hkv, D=D, causal=True, scale=D ** -0.5, eps=1e-5)
+    a = run_block(variant, t, **kw)
+    monkeypatch.setenv("TRINITY_NO_PDL", "1")
+    b = run_block(variant, t, **kw)
+    monkeypatch.delenv("TRINITY_NO_PDL")
+    for k in ("out", "q", "k_cache", "v_cache", "sum_p"):
+        if a[k] is not None:
+            assert torch.equal(a[k], b[k]), k
