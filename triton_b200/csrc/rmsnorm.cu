@@ -75,9 +75,11 @@ rmsnorm_rows_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restr
   }
 }
 
-// Long rows: one CTA of 256 threads per row (grid-stride over rows), each thread keeps its 2-4 vectors
+// Long rows: one CTA of at most 256 threads per row (grid-stride over rows), each thread keeps its 2-4 vectors
 // in registers.  Few registers per thread -> full occupancy -> enough 128-bit loads in flight per SM
 // to cover HBM latency; one __syncthreads per row (the per-warp partial sums are double-buffered).
+// The CTA has just enough warps for the row's vectors at VPT per thread (4 544 columns = 568 vectors: 192 threads x 3
+// instead of 256 x 3 with the third pass three-quarters empty).
 constexpr int kRowCtaThreads = 256;
 
 template <typename T, int VPT>   // VPT: 16-byte vectors per thread
@@ -89,6 +91,7 @@ rmsnorm_cta_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restri
   __shared__ float partial[2][kRowCtaThreads / 32];
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
+  const int nthreads = blockDim.x, nwarps = nthreads >> 5;
   const int nvec = cols >> 3;
   const float inv_cols = 1.0f / static_cast<float>(cols);
   int buf = 0;
@@ -100,7 +103,7 @@ rmsnorm_cta_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restri
     const uint4* xr0 = reinterpret_cast<const uint4*>(x + row0 * x_stride);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int c = tid + i * kRowCtaThreads;
+      const int c = tid + i * nthreads;
       nxt[i] = (row0 < rows && c < nvec) ? __ldcs(xr0 + c) : make_uint4(0u, 0u, 0u, 0u);
     }
   }
@@ -113,7 +116,7 @@ rmsnorm_cta_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restri
       const uint4* xn = reinterpret_cast<const uint4*>(x + rown * x_stride);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
-        const int c = tid + i * kRowCtaThreads;
+        const int c = tid + i * nthreads;
         if (rown < rows && c < nvec) nxt[i] = __ldcs(xn + c);
       }
     }
@@ -133,15 +136,14 @@ rmsnorm_cta_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restri
     if (lane == 0) partial[buf][warp] = ss;
     __syncthreads();
     float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < kRowCtaThreads / 32; ++w) tot += partial[buf][w];
+    for (int w = 0; w < nwarps; ++w) tot += partial[buf][w];
     const float rstd = rsqrtf(tot * inv_cols + eps);
     if (rstd_out != nullptr && tid == 0) rstd_out[row] = rstd;
     if (y == nullptr) continue;
     uint4* yr = reinterpret_cast<uint4*>(y + row * y_stride);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int c = tid + i * kRowCtaThreads;
+      const int c = tid + i * nthreads;
       if (c < nvec) {
         uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
         uint32_t g[4] = {0u, 0u, 0u, 0u};
@@ -227,18 +229,20 @@ int launch_typed(const TrnRmsArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (nvec > 128 && nvec <= 4 * kRowCtaThreads) {
     // rows of 1 K .. 8 K elements (the models' hidden sizes): CTA per row
     const int vpt = (nvec + kRowCtaThreads - 1) / kRowCtaThreads;
+    const int threads = ((nvec + vpt - 1) / vpt + 31) & ~31;       // warps that the row's vectors fill at vpt each
     // one resident wave: grid = SMs x CTAs that fit per SM (asked once per instantiation)
 #define TRN_RMS_CTA(V)                                                                                     \
   do {                                                                                                     \
-    static int per_sm = 0;                                                                                 \
+    static int per_sm_of[kRowCtaThreads / 32 + 1] = {};                                                    \
+    int& per_sm = per_sm_of[threads / 32];                                                                 \
     if (per_sm == 0) {                                                                                     \
       int n = 0;                                                                                           \
-      TRN_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rmsnorm_cta_kernel<T, V>, kRowCtaThreads, 0)); \
+      TRN_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rmsnorm_cta_kernel<T, V>, threads, 0)); \
       per_sm = n > 0 ? n : 1;                                                                              \
     }                                                                                                      \
     const long long cap = static_cast<long long>(ds.sm_count) * per_sm;                                    \
     const int grid = static_cast<int>(a.rows < cap ? a.rows : cap);                                        \
-    rmsnorm_cta_kernel<T, V><<<grid, kRowCtaThreads, 0, st>>>(x, y, g, a.rstd_out, a.rows, cols, a.x_row_stride, \
+    rmsnorm_cta_kernel<T, V><<<grid, threads, 0, st>>>(x, y, g, a.rstd_out, a.rows, cols, a.x_row_stride, \
                                                               a.y_row_stride, a.eps);                      \
   } while (0)
     if (vpt == 1) TRN_RMS_CTA(1);
