@@ -342,6 +342,12 @@ def test_topk_edge_cases():
     assert torch.equal(ops.topk_keys(big, 2048).cpu(), O.topk_keys(big.cpu(), 2048))
     odd = torch.randn(5, 1040, device="cuda")
     assert torch.equal(ops.topk_keys(odd, 1).cpu(), O.topk_keys(odd.cpu(), 1))
+    # every size class of the sort (keys per thread 1 / 2 / 4 / 8, padded and exact powers of two, one warp and less)
+    for n, k in ((1, 1), (7, 3), (32, 32), (33, 5), (500, 499), (1024, 100), (1025, 1025), (2048, 2048), (3000, 17),
+                 (4096, 1024), (5000, 4999), (8192, 8192)):
+        t = torch.randn(4, n, device="cuda")
+        t[2, : n // 2] = 0.25                              # ties over half of a row
+        assert torch.equal(ops.topk_keys(t, k).cpu(), O.topk_keys(t.cpu(), k)), (n, k)
     with pytest.raises(L.TrinityError, match="shape"):
         ops.topk_keys(torch.randn(2, 9000, device="cuda"), 10)
     with pytest.raises(L.TrinityError, match="shape"):
