@@ -228,6 +228,15 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      // A segment's last tile may hold fewer than BN columns (an MQA k / v head: 64 of 256): its MMAs are issued
+      // only as wide as the columns that exist (rounded up to 64; an instruction's cost grows with its N), the
+      // accumulator columns past them are never read
+      uint32_t idesc_t = idesc;
+      if constexpr (FORM == 0) {
+        const TileCoord tcm = decode_tile(p, t);
+        const int n_valid = p.seg[tcm.seg].n - tcm.n_tile * BN;
+        if (n_valid < BN) idesc_t = make_idesc_f16(Io<T>::kFmt, /*a_mn=*/0, /*b_mn=*/1, BM, (n_valid + 63) & ~63);
+      }
       ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, KST_TIMEOUT_MMA);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -247,7 +256,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             const uint64_t adesc = make_smem_desc(sa + kk * 32, 0, 1024);
             // w tile: MN-major, 16 K-rows = 2 KiB; 64-column blocks 8 KiB apart
             const uint64_t bdesc = make_smem_desc(sb + kk * 2048, kBBlockBytes, 1024);
-            umma_ss(d_tmem, adesc, bdesc, idesc, (ks | kk) != 0 ? 1u : 0u);
+            umma_ss(d_tmem, adesc, bdesc, idesc_t, (ks | kk) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));   // frees the stage when these MMAs have read it
         }
