@@ -387,6 +387,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 }
 
 #include "qkv_splitk.cuh"
+#include "qkv_gemm2.cuh"
 
 // Extra operands of the LoRA form: o = x @ wq + d @ b (wk, wv unused).
 struct KcatOperands {
@@ -397,7 +398,7 @@ struct KcatOperands {
 
 template <typename T, int BN, int FORM>
 int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, const KcatOperands* kc = nullptr,
-                 int gate = 0, int n_split = 1, int rows_pad = 0) {
+                 int gate = 0, int n_split = 1, int rows_pad = 0, bool pairs = false) {
   constexpr bool KCAT = (FORM == 1);
   constexpr bool GATED = (FORM == 2);
   GemmParams p{};
@@ -471,6 +472,34 @@ int launch_tiled(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds, c
     if (rc != TRN_OK) return rc;
   }
 
+  if constexpr (BN == 256 && FORM == 0) {
+    if (pairs) {
+      // CTA pairs (qkv_gemm2.cuh): 256 x 256 tiles, one pair of SMs each, persistent over the tiles
+      p.m_tiles = (rows + 2 * BM - 1) / (2 * BM);
+      p.total_tiles = p.m_tiles * p.n_tiles_total;
+      auto pk = qkv_gemm2_kernel<T>;
+      int rc = ensure_dyn_smem(reinterpret_cast<const void*>(pk), kG2SmemBytes, ds.device);
+      if (rc != TRN_OK) return rc;
+      const int max_pairs = ds.sm_count / 2;
+      const int n_pairs = p.total_tiles < max_pairs ? p.total_tiles : max_pairs;
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(static_cast<unsigned>(2 * n_pairs), 1, 1);
+      cfg.blockDim = dim3(kG2Threads, 1, 1);
+      cfg.dynamicSmemBytes = kG2SmemBytes;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = pdl_enabled() ? 2 : 1;
+      TRN_CUDA_TRY(cudaLaunchKernelEx(&cfg, pk, tm_x, tm_w[0], tm_w[1], tm_w[2], p));
+      return TRN_OK;
+    }
+  }
   if constexpr ((BN == 256 || BN == 384) && FORM == 0) {
     if (n_split > 1 || BN == 384) {
       // at most 32 rows: the contraction of every tile split over a cluster of n_split CTAs (qkv_splitk.cuh)
@@ -564,7 +593,10 @@ int launch_typed(const TrnProjArgs& a, cudaStream_t st, const DeviceState& ds) {
   if (n_split > 1 && bn == 384) return launch_tiled<T, 384, 0>(a, st, ds, nullptr, 0, n_split, rows_pad);
   if (n_split > 1) return launch_tiled<T, 256, 0>(a, st, ds, nullptr, 0, n_split, rows_pad);
   if (m_tiles == 1 && n128 <= 2LL * ds.sm_count) return launch_tiled<T, 128, 0>(a, st, ds);
-  return launch_tiled<T, 256, 0>(a, st, ds);
+  // several row tiles: CTA pairs (qkv_gemm2.cuh) once there is a wave of 256 x 256 tiles for the pairs of SMs
+  const long long n256 = (a.Hq * a.D + 255) / 256 + 2LL * ((a.Hkv * a.D + 255) / 256);
+  const bool pairs = ((m_tiles + 1) / 2) * n256 >= ds.sm_count / 2;
+  return launch_tiled<T, 256, 0>(a, st, ds, nullptr, 0, 1, 0, pairs);
 }
 
 bool head_tensor_ok(const TrnHeadTensor& t) {
