@@ -567,7 +567,7 @@ def run_ours(args, w):
         top = max(kern_flops, key=lambda k: kern_us[k])
         ach = kern_flops[top] / (kern_us[top] * 1e-6) / 1e12
         traffic = TRAFFIC_BYTES.get((args.workload, top)) if world == 1 else None
-        line["roofline"] = {"kernel": {"qkv_gemm": "qkv_gemm_kernel", "attention": "attn_fwd_kernel",
+        line["roofline"] = {"kernel": {"qkv_gemm": "qkv_gemm2_kernel (CTA pairs; qkv_gemm_kernel below one wave of 256 x 256 tiles)", "attention": "attn_fwd_kernel",
                                        "attention+perturbed_lse": "attn_fwd_kernel"}[top],
                             "bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s",
                             "frac": ach / peaks["tflops"], "peak_source": peaks["kind"] + " burst",
