@@ -588,7 +588,7 @@ def run_ours(args, w):
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the named kernel at the workload's full
 # size, from ncu captures (None where no capture was taken)
 TRAFFIC_BYTES = {
-    ("prenorm_llama", "qkv_gemm"): 423863808 + 184058112,
+    ("prenorm_llama", "qkv_gemm"): 517946880 + 183176704,
     ("prenorm_llama", "attention"): 297662720 + 102904832,
     "rmsnorm_llama": 134235392 + 81776128,
 }
