@@ -64,6 +64,10 @@ PROJ_CASES = [
     # wider than the device holds clusters of 256-column tiles for: 384-column tiles (1.5 / 3 heads of 128, 6 of 64)
     (1, 16, 8, 512, 64, 64, 128, BF, True, True),
     (2, 10, 0, 640, 128, 128, 64, HF, True, False),
+    # at least a wave of 256 x 256 tiles: the CTA-pair kernel, with a ragged last row tile (the second CTA of the last
+    # pair holds 68 / 1 valid rows), per-head norm + row scale, and a hidden size that is not a multiple of the k step
+    (1, 2500, 12, 512, 8, 4, 128, BF, True, True),
+    (5, 333, 7, 520, 16, 16, 64, HF, False, False),
 ]
 
 
